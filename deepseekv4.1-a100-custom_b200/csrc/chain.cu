@@ -1,0 +1,361 @@
+// MoE layer for a decode batch and the C-ABI entry points of the grouped FP4 / dense FP8 GEMMs.
+//
+// Layer = one routing kernel (input fake quantisation, router, stable bucketing of the (token, expert) pairs by expert,
+// work list) followed by the weight-streaming skinny GEMMs (skinny.cu) with fused epilogues and a final combine.
+#include "common.cuh"
+#include "skinny.cuh"
+#include "router.cuh"
+#include "b200_moe.h"
+
+namespace b200 {
+
+constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
+constexpr int ROUTE_MAX_EXPERTS = 1024;
+
+struct RouteArgs {
+    int tokens, E, topk, dim;
+    const float* logits_f32;
+    const __nv_bfloat16* logits_bf16;
+    const float* bias;
+    float temp, route_scale;
+    int mode, norm;
+    const __nv_bfloat16* x;
+    __nv_bfloat16* xq;  // nullptr: x is already quantised
+    int shard_start, shard_n;
+    int* eid;           // [tokens, topk]
+    float* wt;          // [tokens, topk]
+    int* pair_tok;      // sorted position -> token
+    int* pair_out;      // sorted position -> original pair index t*topk + j
+    float* pair_w;      // sorted position -> routing weight
+    int4* work;
+    int* n_work;
+    unsigned int* counter;
+};
+
+// One block per token: fake-quantise the token's activation (dsv41/quant.py:46-54) and route it (dsv41/model.py:1614-1630).
+// The last block to finish buckets all pairs by expert (stable, the order of dsv41/moe_kernels.py:111-116 and
+// dsv41/decode.py:417-433) and emits the work list of the shard's experts.
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArgs a) {
+    __shared__ float sh_f[8];
+    __shared__ int sh_i[4];
+    __shared__ int is_last;
+    __shared__ int s_eid[ROUTE_MAX_PAIRS];
+    __shared__ int s_cnt[ROUTE_MAX_EXPERTS];
+    __shared__ int s_start[ROUTE_MAX_EXPERTS];
+    __shared__ int s_woff[ROUTE_MAX_EXPERTS];
+    __shared__ int s_scan[ROUTE_THREADS];
+    const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (a.xq) {
+        const int groups = a.dim >> 5;
+        for (int gi = warp; gi < groups; gi += ROUTE_THREADS / 32) {
+            const long off = (long)tok * a.dim + gi * 32 + lane;
+            const float v = __bfloat162float(a.x[off]);
+            const float s = fp8_group_scale(warp_max(fabsf(v)));
+            a.xq[off] = __float2bfloat16_rn(fp8_fake_quant_value(v, s));
+        }
+    }
+    gate_topk_row(a.logits_f32 ? a.logits_f32 + (long)tok * a.E : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.E : nullptr, a.bias, a.E,
+                  a.temp, a.topk, a.route_scale, a.mode, a.norm, a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, sh_f, sh_i);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = (atomicInc(a.counter, gridDim.x - 1) == gridDim.x - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    const int P = a.tokens * a.topk, E = a.E;
+    for (int e = tid; e < E; e += ROUTE_THREADS) s_cnt[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < P; p += ROUTE_THREADS) {
+        const int e = __ldcg(a.eid + p);
+        s_eid[p] = e;
+        atomicAdd(&s_cnt[e], 1);
+    }
+    __syncthreads();
+    // exclusive scans over experts: pair offsets (all experts) and work offsets (this shard's experts)
+    const int per = (E + ROUTE_THREADS - 1) / ROUTE_THREADS;
+    for (int pass = 0; pass < 2; ++pass) {
+        int local = 0;
+        for (int i = 0; i < per; ++i) {
+            const int e = tid * per + i;
+            if (e < E) {
+                const bool mine = e >= a.shard_start && e < a.shard_start + a.shard_n;
+                local += pass == 0 ? s_cnt[e] : (mine ? (s_cnt[e] + SK_TOK - 1) / SK_TOK : 0);
+            }
+        }
+        s_scan[tid] = local;
+        __syncthreads();
+        if (tid == 0) {
+            int run = 0;
+            for (int i = 0; i < ROUTE_THREADS; ++i) { int v = s_scan[i]; s_scan[i] = run; run += v; }
+            if (pass == 1) *a.n_work = run;
+        }
+        __syncthreads();
+        int run = s_scan[tid];
+        for (int i = 0; i < per; ++i) {
+            const int e = tid * per + i;
+            if (e < E) {
+                const bool mine = e >= a.shard_start && e < a.shard_start + a.shard_n;
+                if (pass == 0) { s_start[e] = run; run += s_cnt[e]; }
+                else { s_woff[e] = run; run += mine ? (s_cnt[e] + SK_TOK - 1) / SK_TOK : 0; }
+            }
+        }
+        __syncthreads();
+    }
+    // stable placement: the thread that owns expert e walks the pairs in index order
+    for (int e = tid; e < E; e += ROUTE_THREADS) {
+        const int cnt = s_cnt[e];
+        if (cnt == 0) continue;
+        int pos = s_start[e];
+        for (int p = 0; p < P; ++p) {
+            if (s_eid[p] == e) {
+                a.pair_tok[pos] = p / a.topk;
+                a.pair_out[pos] = p;
+                a.pair_w[pos] = __ldcg(a.wt + p);
+                ++pos;
+            }
+        }
+        if (e >= a.shard_start && e < a.shard_start + a.shard_n) {
+            const int nsub = (cnt + SK_TOK - 1) / SK_TOK;
+            for (int i = 0; i < nsub; ++i) {
+                const int rem = cnt - i * SK_TOK;
+                a.work[s_woff[e] + i] = make_int4(e - a.shard_start, s_start[e] + i * SK_TOK, rem < SK_TOK ? rem : SK_TOK, e);
+            }
+        }
+    }
+}
+
+// out[t, n] = bf16( sum over the token's LOCAL experts of y2[t*topk + j, n] + float(ys[t, n]) )  (dsv41/fused2.py:518-523);
+// routed[t, n] (optional) = the fp32 routed sum alone (what an expert-parallel rank sends back, dsv41/ep.py:431-435).
+__global__ void moe_combine_kernel(const float* __restrict__ y2, const int* __restrict__ eid, const __nv_bfloat16* __restrict__ ys,
+                                   __nv_bfloat16* __restrict__ out, float* __restrict__ routed, int tokens, int topk, int dim, int shard_start,
+                                   int shard_n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)tokens * dim) return;
+    const int t = (int)(i / dim), n = (int)(i % dim);
+    float acc = 0.f;
+    for (int j = 0; j < topk; ++j) {
+        const int e = eid[t * topk + j];
+        if (e >= shard_start && e < shard_start + shard_n) acc += y2[((long)t * topk + j) * dim + n];
+    }
+    if (routed) routed[i] = acc;
+    if (out) out[i] = __float2bfloat16_rn(acc + (ys ? __bfloat162float(ys[i]) : 0.f));
+}
+
+struct Carver {
+    char* p;
+    size_t left;
+    bool ok = true;
+    template <typename T>
+    T* take(size_t n) {
+        size_t bytes = (n * sizeof(T) + 255) & ~(size_t)255;
+        if (bytes > left) { ok = false; return nullptr; }
+        T* r = reinterpret_cast<T*>(p);
+        p += bytes;
+        left -= bytes;
+        return r;
+    }
+};
+
+static size_t rnd256(size_t b) { return (b + 255) & ~(size_t)255; }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_version(void) { return 100; }
+
+extern "C" int b200_sm_count(void) { return sm_count(); }
+
+extern "C" const char* b200_error_string(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case ERR_BAD_ARG: return "b200: bad argument (null pointer or non-positive size)";
+        case ERR_BAD_SHAPE: return "b200: shape violates a divisibility or range rule";
+        case ERR_BAD_ALIGN: return "b200: pointer or stride misaligned";
+        case ERR_WORKSPACE: return "b200: workspace too small";
+        case ERR_UNSUPPORTED: return "b200: unsupported format or mode";
+        case ERR_TOO_LARGE: return "b200: size beyond the fixed maximum of this entry point";
+    }
+    if (code > 0) return cudaGetErrorString((cudaError_t)code);
+    return "b200: unknown error";
+}
+
+// ------------------------------------------------------------------ grouped FP4 GEMM
+extern "C" size_t b200_fp4_grouped_workspace_bytes(int n_pairs) {
+    if (n_pairs < 0) n_pairs = 0;
+    return rnd256((size_t)(n_pairs + 1) * sizeof(int4)) + 256;
+}
+
+extern "C" int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s,
+                                     long long s_estride, int fmt, int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count,
+                                     int n_groups, const int* pair_tok, const int* pair_out, const float* pair_w, int n_pairs, int shard_start, int shard_n,
+                                     int zero_out, int accumulate, float* out, long long out_ld, void* workspace, size_t workspace_bytes,
+                                     cudaStream_t stream) {
+    if (!x || !w || !s || !grp_expert || !grp_start || !out || !workspace || n_groups < 0 || n_pairs < 0) return ERR_BAD_ARG;
+    if (fmt != SK_FMT_FP4_E8M0 && fmt != SK_FMT_FP4_BF16S) return ERR_UNSUPPORTED;
+    if (workspace_bytes < b200_fp4_grouped_workspace_bytes(n_pairs) || ((uintptr_t)workspace & 15)) return ERR_WORKSPACE;
+    if (n_pairs == 0 || n_groups == 0) return 0;
+    Carver cv{(char*)workspace, workspace_bytes};
+    int4* work = cv.take<int4>((size_t)n_pairs + 1);
+    int* n_work = cv.take<int>(1);
+    if (!cv.ok) return ERR_WORKSPACE;
+    SkinnyArgs a{};
+    a.w = (const uint8_t*)w; a.w_estride = w_estride;
+    a.s = (const uint8_t*)s; a.s_estride = s_estride;
+    a.s_rstride = (K / 32) * (fmt == SK_FMT_FP4_BF16S ? 2 : 1);
+    a.N = N; a.K = K;
+    a.x = (const __nv_bfloat16*)x; a.x_ld = x_ld; a.x_perm8 = x_perm8;
+    a.work = work; a.n_work = n_work;
+    a.pair_tok = pair_tok; a.pair_out = pair_out; a.pair_w = pair_w;
+    a.out = out; a.out_ld = out_ld;
+    const int epi = accumulate ? SK_EPI_ATOMIC_F32 : SK_EPI_STORE_F32;
+    int rc = skinny_check(a, fmt, epi);
+    if (rc) return rc;
+    if (shard_n > (1 << 29)) shard_n = 1 << 29;
+    rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, work, n_work, n_pairs, stream);
+    if (rc) return rc;
+    if (zero_out && !accumulate) {
+        rc = skinny_zero_foreign(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, out, out_ld, N, stream);
+        if (rc) return rc;
+    }
+    return skinny_launch(a, fmt, epi, stream);
+}
+
+// ------------------------------------------------------------------ dense FP8
+extern "C" int b200_fp8_gemm(const void* x, long long x_ld, int M, const void* w8, const void* s, int fmt, int s_cols, int w_permk, int N, int K,
+                             void* out, int out_is_f32, long long out_ld, cudaStream_t stream) {
+    if (!x || !w8 || !s || !out || M < 0 || s_cols <= 0) return ERR_BAD_ARG;
+    if (fmt != SK_FMT_FP8_E8M0 && fmt != SK_FMT_FP8_F32B) return ERR_UNSUPPORTED;
+    if (fmt == SK_FMT_FP8_E8M0 ? s_cols < K / 32 : s_cols < (K + 127) / 128) return ERR_BAD_SHAPE;
+    if (M == 0) return 0;
+    SkinnyArgs a{};
+    a.w = (const uint8_t*)w8; a.w_estride = 0;
+    a.s = (const uint8_t*)s; a.s_estride = 0;
+    a.s_rstride = fmt == SK_FMT_FP8_E8M0 ? s_cols : s_cols * 4;
+    a.N = N; a.K = K;
+    a.x = (const __nv_bfloat16*)x; a.x_ld = x_ld; a.w_permk = w_permk;
+    a.work = nullptr; a.dense_rows = M; a.n_work = nullptr; a.n_work_host = (M + SK_TOK - 1) / SK_TOK;
+    a.out = out; a.out_ld = out_ld;
+    return skinny_launch(a, fmt, out_is_f32 ? SK_EPI_STORE_F32 : SK_EPI_STORE_BF16, stream);
+}
+
+// ------------------------------------------------------------------ whole layer
+extern "C" size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter) {
+    if (tokens < 0 || topk < 0 || dim < 0 || inter < 0) return 0;
+    const size_t P = (size_t)tokens * topk;
+    size_t b = 0;
+    b += rnd256((size_t)tokens * dim * 2);  // xq
+    b += rnd256(P * 4) * 2;                 // eid, wt
+    b += rnd256(P * 4) * 3;                 // pair_tok, pair_out, pair_w
+    b += rnd256((P + 1) * 16);              // work
+    b += rnd256(4) * 2;                     // n_work, counter
+    b += rnd256(P * inter * 2);             // hq
+    b += rnd256((size_t)tokens * inter * 2);  // hs
+    b += rnd256(P * dim * 4);               // y2
+    b += rnd256((size_t)tokens * dim * 2);  // ys
+    return b + 256;
+}
+
+extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
+    if (!m || !m->logits || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
+    if (m->tokens < 0 || m->topk < 1 || m->n_experts < 1 || m->dim < 1 || m->inter < 1) return ERR_BAD_ARG;
+    if (m->has_shared && (!m->sh_w13 || !m->sh_s13 || !m->sh_w2 || !m->sh_s2)) return ERR_BAD_ARG;
+    if (m->tokens == 0) return 0;
+    const int T = m->tokens, topk = m->topk, D = m->dim, I = m->inter, E = m->n_experts;
+    const long P = (long)T * topk;
+    if (P > ROUTE_MAX_PAIRS || E > ROUTE_MAX_EXPERTS || topk > 32 || topk > E) return ERR_BAD_SHAPE;
+    if (D % 128 || I % 128) return ERR_BAD_SHAPE;
+    if (m->expert_fmt != SK_FMT_FP4_E8M0 && m->expert_fmt != SK_FMT_FP4_BF16S) return ERR_UNSUPPORTED;
+    if (m->has_shared && m->shared_fmt != SK_FMT_FP8_E8M0 && m->shared_fmt != SK_FMT_FP8_F32B) return ERR_UNSUPPORTED;
+    if (m->score_mode < 0 || m->score_mode > 2) return ERR_UNSUPPORTED;
+    if (m->workspace_bytes < b200_moe_workspace_bytes(T, topk, D, I) || ((uintptr_t)m->workspace & 255)) return ERR_WORKSPACE;
+    int shard_n = m->shard_n > (1 << 29) ? (1 << 29) : m->shard_n;
+    if (m->shard_start < 0 || shard_n < 0) return ERR_BAD_ARG;
+
+    Carver cv{(char*)m->workspace, m->workspace_bytes};
+    __nv_bfloat16* xq = cv.take<__nv_bfloat16>((size_t)T * D);
+    int* eid = cv.take<int>(P);
+    float* wt = cv.take<float>(P);
+    int* pair_tok = cv.take<int>(P);
+    int* pair_out = cv.take<int>(P);
+    float* pair_w = cv.take<float>(P);
+    int4* work = cv.take<int4>(P + 1);
+    int* n_work = cv.take<int>(1);
+    unsigned int* counter = cv.take<unsigned int>(1);
+    __nv_bfloat16* hq = cv.take<__nv_bfloat16>((size_t)P * I);
+    __nv_bfloat16* hs = cv.take<__nv_bfloat16>((size_t)T * I);
+    float* y2 = cv.take<float>((size_t)P * D);
+    __nv_bfloat16* ys = cv.take<__nv_bfloat16>((size_t)T * D);
+    if (!cv.ok) return ERR_WORKSPACE;
+
+    // the counter of the "last block" election must start at zero; it resets itself after every launch
+    cudaError_t ce = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
+    if (ce != cudaSuccess) return (int)ce;
+
+    RouteArgs r{};
+    r.tokens = T; r.E = E; r.topk = topk; r.dim = D;
+    r.logits_f32 = m->logits_is_bf16 ? nullptr : (const float*)m->logits;
+    r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
+    r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
+    r.x = (const __nv_bfloat16*)m->x; r.xq = m->x_is_quantized ? nullptr : xq;
+    r.shard_start = m->shard_start; r.shard_n = shard_n;
+    r.eid = eid; r.wt = wt; r.pair_tok = pair_tok; r.pair_out = pair_out; r.pair_w = pair_w; r.work = work; r.n_work = n_work; r.counter = counter;
+    moe_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
+    B200_CHECK_LAUNCH();
+    const __nv_bfloat16* xin = m->x_is_quantized ? (const __nv_bfloat16*)m->x : xq;
+    const int sbytes = m->expert_fmt == SK_FMT_FP4_BF16S ? 2 : 1;
+
+    // routed gate/up + SwiGLU * weight + fake quant -> hq [sorted pair, inter]
+    SkinnyArgs a{};
+    a.w = (const uint8_t*)m->w13; a.w_estride = (long long)2 * I * (D / 2);
+    a.s = (const uint8_t*)m->s13; a.s_estride = (long long)2 * I * (D / 32) * sbytes; a.s_rstride = (D / 32) * sbytes;
+    a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = D;
+    a.work = work; a.n_work = n_work; a.pair_tok = pair_tok; a.pair_out = nullptr; a.pair_w = pair_w;
+    a.out = hq; a.out_ld = I; a.limit = m->swiglu_limit; a.inter = I;
+    int rc = skinny_launch(a, m->expert_fmt, SK_EPI_SWIGLU, stream);
+    if (rc) return rc;
+    // routed down -> y2 [original pair, dim] fp32
+    SkinnyArgs b{};
+    b.w = (const uint8_t*)m->w2; b.w_estride = (long long)D * (I / 2);
+    b.s = (const uint8_t*)m->s2; b.s_estride = (long long)D * (I / 32) * sbytes; b.s_rstride = (I / 32) * sbytes;
+    b.N = D; b.K = I; b.x = hq; b.x_ld = I;
+    b.work = work; b.n_work = n_work; b.pair_tok = nullptr; b.pair_out = pair_out; b.pair_w = nullptr;
+    b.out = y2; b.out_ld = D;
+    rc = skinny_launch(b, m->expert_fmt, SK_EPI_STORE_F32, stream);
+    if (rc) return rc;
+    if (m->has_shared && m->out) {
+        // shared expert: gu rounded to bf16, SwiGLU without weight, fake quant, down projection rounded to bf16 (dsv41/decode.py:461-463)
+        SkinnyArgs c{};
+        c.w = (const uint8_t*)m->sh_w13; c.s = (const uint8_t*)m->sh_s13;
+        c.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s13_cols : m->sh_s13_cols * 4;
+        c.N = 2 * I; c.K = D; c.x = xin; c.x_ld = D; c.w_permk = m->sh_permk;
+        c.work = nullptr; c.dense_rows = T; c.n_work_host = (T + SK_TOK - 1) / SK_TOK;
+        c.out = hs; c.out_ld = I; c.limit = m->swiglu_limit; c.inter = I; c.round_gu_bf16 = 1;
+        rc = skinny_launch(c, m->shared_fmt, SK_EPI_SWIGLU, stream);
+        if (rc) return rc;
+        SkinnyArgs d{};
+        d.w = (const uint8_t*)m->sh_w2; d.s = (const uint8_t*)m->sh_s2;
+        d.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s2_cols : m->sh_s2_cols * 4;
+        d.N = D; d.K = I; d.x = hs; d.x_ld = I; d.w_permk = m->sh_permk;
+        d.work = nullptr; d.dense_rows = T; d.n_work_host = (T + SK_TOK - 1) / SK_TOK;
+        d.out = ys; d.out_ld = D;
+        rc = skinny_launch(d, m->shared_fmt, SK_EPI_STORE_BF16, stream);
+        if (rc) return rc;
+    }
+    const long n = (long)T * D;
+    moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y2, eid, (m->has_shared && m->out) ? ys : nullptr, (__nv_bfloat16*)m->out,
+                                                                       m->routed_out, T, topk, D, m->shard_start, shard_n);
+    B200_CHECK_LAUNCH();
+    if (m->eid_out) {
+        ce = cudaMemcpyAsync(m->eid_out, eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream);
+        if (ce != cudaSuccess) return (int)ce;
+    }
+    if (m->wt_out) {
+        ce = cudaMemcpyAsync(m->wt_out, wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream);
+        if (ce != cudaSuccess) return (int)ce;
+    }
+    return 0;
+}

@@ -1,0 +1,53 @@
+// Internal interface of the weight-streaming skinny GEMM (skinny.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int SK_THREADS = 512;         // 16 warps: 4 row blocks x 4 splits of K
+constexpr int SK_ROWS = 64;             // weight rows per item
+constexpr int SK_TOK = 8;               // token columns per work (one 8-wide tensor-core tile)
+constexpr int SK_CHUNKS_PER_BATCH = 4;  // 16-byte loads per row in flight per lane
+constexpr int SK_RED_BYTES = 2 * 4 * 4 * 16 * 8 * 4;
+
+// weight formats (also the `fmt` values of the C-ABI)
+enum { SK_FMT_FP4_E8M0 = 0, SK_FMT_FP4_BF16S = 1, SK_FMT_FP8_E8M0 = 2, SK_FMT_FP8_F32B = 3 };
+// epilogues
+enum { SK_EPI_STORE_F32 = 0, SK_EPI_ATOMIC_F32 = 1, SK_EPI_SWIGLU = 2, SK_EPI_STORE_BF16 = 3 };
+
+struct SkinnyArgs {
+    const uint8_t* w;       // weights: [experts][N][K/2] packed E2M1 or [experts][N][K] e4m3
+    long long w_estride;    // bytes between experts
+    const uint8_t* s;       // scales (format dependent)
+    long long s_estride;    // bytes between experts
+    int s_rstride;          // bytes between scale rows (FP4: per weight row; FP8: per 32- or 128-row block)
+    int N, K;
+    const __nv_bfloat16* x; // activations, row-major
+    long long x_ld;         // elements between rows
+    int x_perm8;            // x is in the 8-k permuted layout of dsv41/cukern.py:267-273
+    int w_permk;            // FP8 weight bytes are in the 16-k order of dsv41/w8.py:21-23
+    const int4* work;       // {local expert, first pair, n pairs (1..8), group}; nullptr = dense mode over dense_rows
+    int dense_rows;
+    const int* n_work;      // device count of works, or nullptr to use n_work_host
+    int n_work_host;
+    const int* pair_tok;    // x row of each pair (nullptr: the pair index)
+    const int* pair_out;    // output row of each pair (nullptr: the pair index)
+    const float* pair_w;    // optional weight per pair
+    void* out;
+    long long out_ld;       // elements between output rows
+    float limit;            // SwiGLU clamp (epilogue SK_EPI_SWIGLU)
+    int inter;              // N == 2*inter for SK_EPI_SWIGLU
+    int round_gu_bf16;      // round gate/up to bf16 before SwiGLU (shared expert)
+};
+
+int sm_count();
+int skinny_check(const SkinnyArgs& a, int fmt, int epi);
+int skinny_launch(const SkinnyArgs& a, int fmt, int epi, cudaStream_t stream);
+int skinny_plan(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n, int4* work,
+                int* n_work, int max_work, cudaStream_t stream);
+int skinny_zero_foreign(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n,
+                        float* out, long long out_ld, int N, cudaStream_t stream);
+
+}  // namespace b200

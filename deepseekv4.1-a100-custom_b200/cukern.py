@@ -1,0 +1,160 @@
+"""Launchers of the CUDA kernels, with the names, argument order and dtypes of the reference's dsv41/cukern.py so that
+its callers (decode.experts_tc, MoE.__call__, EPRuntime) can use them unchanged.  Every launcher allocates its own output
+unless `out=` is given, launches on the current torch stream of the tensor's device and never synchronises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib as L
+
+_PERM8 = [0, 4, 2, 6, 1, 5, 3, 7]
+FP4_W_MAX = 64  # tokens per group the reference's bucketing produces (dsv41/cukern.py:276-277); any size is accepted here
+
+
+def _i32(t: torch.Tensor | None, dev) -> torch.Tensor | None:
+    if t is None:
+        return None
+    return t.to(device=dev, dtype=torch.int32).contiguous()
+
+
+def _fp4_fmt(s: torch.Tensor) -> int:
+    if s.dtype == torch.uint8:
+        return L.FMT_FP4_E8M0
+    if s.dtype == torch.bfloat16:
+        return L.FMT_FP4_BF16S
+    raise TypeError(f"expert scales must be uint8 (E8M0) or bfloat16, got {s.dtype}")
+
+
+def grouped_fp4(x, w, s, grp_expert, grp_start, grp_count, pair_tok, pair_out, pair_w, n_pairs, *, x_perm8=False, shard_start=0,
+                shard_n=1 << 30, zero_out=False, accumulate=False, out=None, n_out_rows=None):
+    """Common launcher of b200_fp4_grouped_gemm (see include/b200_moe.h)."""
+    dev = L.require_cuda(x, w, s, grp_expert, grp_start, out)
+    E, N, Kh = w.shape
+    K = Kh * 2
+    assert x.dtype == torch.bfloat16 and x.stride(-1) == 1 and x.dim() == 2 and x.shape[1] == K
+    assert w.dtype == torch.uint8 and w.is_contiguous() and s.is_contiguous() and s.shape == (E, N, K // 32)
+    if out is None:
+        rows = n_pairs if n_out_rows is None else n_out_rows
+        out = (torch.zeros if accumulate else torch.empty)(rows, N, device=dev, dtype=torch.float32)
+    assert out.dtype == torch.float32 and out.stride(-1) == 1
+    ge, gs, gc = _i32(grp_expert, dev), _i32(grp_start, dev), _i32(grp_count, dev)
+    pt, po = _i32(pair_tok, dev), _i32(pair_out, dev)
+    pw = pair_w.to(device=dev, dtype=torch.float32).contiguous() if pair_w is not None else None
+    G = ge.numel()
+    assert gs.numel() >= (G if gc is not None else G + 1)
+    lib = L.lib()
+    nbytes = lib.b200_fp4_grouped_workspace_bytes(int(n_pairs))
+    ws = L.workspace(dev, nbytes, "fp4_grouped")
+    with torch.cuda.device(dev):
+        rc = lib.b200_fp4_grouped_gemm(L.ptr(x), x.stride(0), int(bool(x_perm8)), L.ptr(w), w.stride(0) * w.element_size(), L.ptr(s),
+                                       s.stride(0) * s.element_size(), _fp4_fmt(s), N, K, L.ptr(ge), L.ptr(gs), L.ptr(gc), G, L.ptr(pt), L.ptr(po),
+                                       L.ptr(pw), int(n_pairs), int(shard_start), int(min(shard_n, 1 << 30)), int(bool(zero_out)),
+                                       int(bool(accumulate)), L.ptr(out), out.stride(0), L.ptr(ws), ws.numel(), L.stream_of(dev))
+    L.check(rc, "b200_fp4_grouped_gemm")
+    return out
+
+
+_arange_cache: dict = {}
+
+
+def _arange(n: int, dev) -> torch.Tensor:
+    key = (n, dev)
+    t = _arange_cache.get(key)
+    if t is None:
+        t = _arange_cache[key] = torch.arange(n, device=dev, dtype=torch.int32)
+    return t
+
+
+def fp4_gemv_pairs(x: torch.Tensor, w: torch.Tensor, s: torch.Tensor, row_in: torch.Tensor, expert: torch.Tensor, wt: torch.Tensor,
+                   n_pairs: int) -> torch.Tensor:
+    """x bf16 [rows_in, K]; w uint8 [E, N, K/2]; s uint8 [E, N, K/32]; row_in / expert int32 [pairs]; wt fp32 [pairs].
+    Returns fp32 [pairs, N] = wt * x[row_in] @ W[expert]^T  (dsv41/cukern.py:60-77): one group per pair."""
+    return grouped_fp4(x, w, s, expert, _arange(n_pairs + 1, x.device), None, row_in, None, wt, n_pairs)
+
+
+def fp4_gemm_tc(xp: torch.Tensor, w: torch.Tensor, s: torch.Tensor, grp_expert: torch.Tensor, grp_start: torch.Tensor, pair_tok: torch.Tensor,
+                n_pairs: int, max_tokens: int, shard_start: int = 0, shard_n: int = 1 << 30, zero_out: bool = False,
+                out: torch.Tensor | None = None, min_tokens: int = 0) -> torch.Tensor:
+    """xp: 8-k PERMUTED bf16 [rows, K] (permute_x); groups g: expert grp_expert[g] (global id, -1 = padding) with pairs
+    grp_start[g] .. grp_start[g+1]-1, pair p reads x row pair_tok[p].  Returns fp32 [n_pairs, N].  Groups outside
+    [shard_start, shard_start + shard_n) are skipped (zero_out: rows zeroed)  (dsv41/cukern.py:309-344).  max_tokens and
+    min_tokens are accepted for compatibility; every group size runs on the same kernel."""
+    assert xp.is_contiguous()
+    return grouped_fp4(xp, w, s, grp_expert, grp_start, None, pair_tok, None, None, n_pairs, x_perm8=True, shard_start=shard_start, shard_n=shard_n,
+                       zero_out=zero_out, out=out)
+
+
+def fp4_gemv_m1(xp, w, s, grp_expert, grp_start, pair_tok, n_pairs, shard_start=0, shard_n=1 << 30, zero_out=False, out=None, kw=None, u=None):
+    """One-token groups of a grouped expert GEMM (dsv41/cukern.py:286-306).  Same kernel as fp4_gemm_tc here; kw / u ignored."""
+    return fp4_gemm_tc(xp, w, s, grp_expert, grp_start, pair_tok, n_pairs, 1, shard_start, shard_n, zero_out, out)
+
+
+def permute_x(x: torch.Tensor) -> torch.Tensor:
+    """bf16 [M, K] -> 8-k permuted copy (within every 8 k: 0,4,2,6,1,5,3,7)  (dsv41/cukern.py:270-273)."""
+    dev = L.require_cuda(x)
+    assert x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    with torch.cuda.device(dev):
+        L.check(L.lib().b200_permute_x8(L.ptr(xc), L.ptr(y), xc.numel(), L.stream_of(dev)), "b200_permute_x8")
+    return y
+
+
+# --------------------------------------------------------------------------- FP8 dense
+def _fp8(x, w8, s8, w_permk: bool, out_dtype, out=None):
+    dev = L.require_cuda(x, w8, s8, out)
+    M, K = x.shape
+    N = w8.shape[0]
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and w8.is_contiguous() and s8.is_contiguous() and w8.shape[1] == K
+    w8 = w8.view(torch.uint8)
+    if s8.dtype == torch.uint8:
+        fmt = L.FMT_FP8_E8M0
+    elif s8.dtype == torch.float32:
+        fmt = L.FMT_FP8_F32B
+    else:
+        raise TypeError(f"FP8 scales must be uint8 (E8M0 32x32) or float32 (128x128), got {s8.dtype}")
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    if out is None:
+        out = torch.empty(M, N, device=dev, dtype=out_dtype)
+    assert out.dtype == out_dtype and out.stride(-1) == 1
+    with torch.cuda.device(dev):
+        rc = L.lib().b200_fp8_gemm(L.ptr(x), x.stride(0), M, L.ptr(w8), L.ptr(s8), fmt, s8.shape[1], int(bool(w_permk)), N, K, L.ptr(out),
+                                   int(out_dtype == torch.float32), out.stride(0), L.stream_of(dev))
+    L.check(rc, "b200_fp8_gemm")
+    return out
+
+
+def fp8_gemv(x: torch.Tensor, w_fp8: torch.Tensor, s_u8: torch.Tensor) -> torch.Tensor:
+    """x bf16 [1, K]; w_fp8 float8_e4m3fn/uint8 [N, K] in NATURAL k order; s_u8 uint8 [ceil(N/32), K/32] -> fp32 [1, N]
+    (dsv41/cukern.py:80-96)."""
+    return _fp8(x, w_fp8, s_u8, False, torch.float32)
+
+
+def fp8_gemv_m1(x: torch.Tensor, w8: torch.Tensor, s8: torch.Tensor, group_cols: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One-row FP8 GEMV, weights in the w8.PERM_K byte order -> bf16 [1, N]  (dsv41/cukern.py:116-133)."""
+    if group_cols:
+        raise NotImplementedError("block-diagonal use (attention o-projection) is outside the MoE path")
+    return _fp8(x, w8, s8, True, torch.bfloat16, out)
+
+
+def fp8_gemm_tc(x: torch.Tensor, w8: torch.Tensor, s8: torch.Tensor, group_cols: int = 0, out_dtype=torch.bfloat16, permuted: bool = True) -> torch.Tensor:
+    """x bf16 [M, K]; w8 uint8 e4m3 [N, K] in the w8.PERM_K byte order (permuted=False: natural order); s8 uint8 E8M0
+    [ceil(N/32), K/32] or fp32 [ceil(N/128), ceil(K/128)].  Returns x @ dequant(w8, s8)^T as [M, N]  (dsv41/cukern.py:165-221)."""
+    if group_cols:
+        raise NotImplementedError("block-diagonal use (attention o-projection) is outside the MoE path")
+    assert x.is_contiguous()
+    return _fp8(x, w8, s8, permuted, out_dtype)
+
+
+# --------------------------------------------------------------------------- expert-parallel helpers
+def p2p_sum_rows(dst: torch.Tensor, src: torch.Tensor, device: torch.device, groups: int = 1, dst_stride: int | None = None):
+    """dst[g] = sum of the `rows` rows of group g of src fp32 [groups * rows, n]; dst may live on a peer GPU
+    (dsv41/cukern.py:370-379)."""
+    total, n = src.shape
+    rows = total // groups
+    if dst_stride is None:
+        dst_stride = dst.stride(0) if dst.dim() > 1 else n
+    assert src.dtype == torch.float32 and dst.dtype == torch.float32 and src.is_contiguous()
+    with torch.cuda.device(device):
+        L.check(L.lib().b200_sum_rows(L.ptr(dst), L.ptr(src), rows, n, groups, int(dst_stride), L.stream_of(device)), "b200_sum_rows")

@@ -1,0 +1,86 @@
+"""The MoE layer as one object: routed FP4 experts (optionally one shard of them), the FP8 shared expert and the router
+parameters, with `forward` = router -> input fake quantisation -> expert chain -> combine in a single C-ABI call
+(b200_moe_forward).  Mirrors what the reference's MoE.__call__ (dsv41/model.py:2028-2233) and DecodeRuntime.moe2
+(dsv41/decode.py:446-464) compute for a batch of tokens."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib as L
+from .w8 import W8
+
+
+class MoELayer:
+    def __init__(self, w13: torch.Tensor, s13: torch.Tensor, w2: torch.Tensor, s2: torch.Tensor, *, n_experts: int | None = None, topk: int = 6,
+                 sh_w13: W8 | None = None, sh_w2: W8 | None = None, gate_bias: torch.Tensor | None = None, gate_temp: float = 1.0,
+                 route_scale: float = 1.0, score_func: str = "softmax", norm_topk_prob: bool = True, swiglu_limit: float = 10.0,
+                 shard_start: int = 0):
+        """w13 uint8 [n, 2I, D/2], s13 [n, 2I, D/32] (uint8 E8M0 or bf16), w2 uint8 [n, D, I/2], s2 [n, D, I/32]: the n experts
+        [shard_start, shard_start + n) of a layer with n_experts experts (shard dict of dsv41/load.py:213-232)."""
+        dev = L.require_cuda(w13, s13, w2, s2, gate_bias)
+        n, n13, dh = w13.shape
+        self.dim, self.inter = dh * 2, n13 // 2
+        self.n_local, self.shard_start = n, shard_start
+        self.n_experts = n if n_experts is None else n_experts
+        assert w2.shape == (n, self.dim, self.inter // 2) and s13.shape == (n, n13, self.dim // 32) and s2.shape == (n, self.dim, self.inter // 32)
+        assert s13.dtype == s2.dtype and s13.dtype in (torch.uint8, torch.bfloat16)
+        self.w13, self.s13, self.w2, self.s2 = (t.contiguous() for t in (w13, s13, w2, s2))
+        self.expert_fmt = L.FMT_FP4_E8M0 if s13.dtype == torch.uint8 else L.FMT_FP4_BF16S
+        assert (sh_w13 is None) == (sh_w2 is None)
+        self.sh_w13, self.sh_w2 = sh_w13, sh_w2
+        if sh_w13 is not None:
+            assert sh_w13.shape == (2 * self.inter, self.dim) and sh_w2.shape == (self.dim, self.inter) and sh_w13.s8.dtype == sh_w2.s8.dtype
+        self.topk, self.gate_bias, self.gate_temp, self.route_scale = topk, gate_bias, gate_temp, route_scale
+        self.score_func, self.norm, self.swiglu_limit = score_func, norm_topk_prob and topk > 1, swiglu_limit
+        self.device = dev
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, *, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
+                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True):
+        """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E].
+        Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
+        and (eid, wt)."""
+        dev = L.require_cuda(x, logits, out)
+        assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.is_contiguous()
+        T = x.shape[0]
+        assert logits.shape == (T, self.n_experts) and logits.dtype in (torch.float32, torch.bfloat16) and logits.is_contiguous()
+        lib = L.lib()
+        if final and out is None:
+            out = torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16)
+        routed = torch.empty(T, self.dim, device=dev, dtype=torch.float32) if want_routed else None
+        eid = torch.empty(T, self.topk, device=dev, dtype=torch.int32) if want_route else None
+        wt = torch.empty(T, self.topk, device=dev, dtype=torch.float32) if want_route else None
+        nbytes = lib.b200_moe_workspace_bytes(T, self.topk, self.dim, self.inter)
+        ws = L.workspace(dev, nbytes, "moe")
+        a = L.MoeArgs()
+        a.tokens, a.n_experts, a.topk, a.dim, a.inter = T, self.n_experts, self.topk, self.dim, self.inter
+        a.logits, a.logits_is_bf16 = logits.data_ptr(), int(logits.dtype == torch.bfloat16)
+        a.gate_bias = self.gate_bias.data_ptr() if self.gate_bias is not None else None
+        a.temp, a.route_scale = float(self.gate_temp), float(self.route_scale)
+        a.score_mode, a.norm = L.SCORE_MODES[self.score_func], int(self.norm)
+        a.x, a.x_is_quantized = x.data_ptr(), int(x_is_quantized)
+        a.w13, a.s13, a.w2, a.s2 = self.w13.data_ptr(), self.s13.data_ptr(), self.w2.data_ptr(), self.s2.data_ptr()
+        a.expert_fmt, a.shard_start, a.shard_n = self.expert_fmt, self.shard_start, self.n_local
+        shared = with_shared and self.sh_w13 is not None and final
+        a.has_shared = int(shared)
+        if shared:
+            a.sh_w13, a.sh_s13, a.sh_w2, a.sh_s2 = self.sh_w13.w8.data_ptr(), self.sh_w13.s8.data_ptr(), self.sh_w2.w8.data_ptr(), self.sh_w2.s8.data_ptr()
+            a.shared_fmt = L.FMT_FP8_E8M0 if self.sh_w13.s8.dtype == torch.uint8 else L.FMT_FP8_F32B
+            a.sh_s13_cols, a.sh_s2_cols, a.sh_permk = self.sh_w13.s8.shape[1], self.sh_w2.s8.shape[1], 1
+        a.swiglu_limit = float(self.swiglu_limit)
+        a.out = out.data_ptr() if final else None
+        a.routed_out = routed.data_ptr() if routed is not None else None
+        a.eid_out = eid.data_ptr() if eid is not None else None
+        a.wt_out = wt.data_ptr() if wt is not None else None
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        with torch.cuda.device(dev):
+            L.check(lib.b200_moe_forward(ctypes.byref(a), L.stream_of(dev)), "b200_moe_forward")
+        res = [out] if final else []
+        if want_routed:
+            res.append(routed)
+        if want_route:
+            res += [eid, wt]
+        return res[0] if len(res) == 1 else tuple(res)
+
+    __call__ = forward

@@ -1,0 +1,154 @@
+/*
+ * C-ABI of libb200moe: the sm_100a implementation of the packed-FP4 MoE expert chain and the block-scaled FP8
+ * dense GEMV/GEMM of the DeepSeek-V4.1 A100 runtime, for NVIDIA B200.
+ *
+ * Conventions (the ones dsv41/cukern.py:1-57 sets for the reference's launchers):
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless the comment says "host";
+ *   - every call only enqueues work on `stream`; nothing synchronises, nothing allocates, so calls are
+ *     capturable in a CUDA graph.  Scratch memory is passed in by the caller (`workspace`), sized by the
+ *     matching *_workspace_bytes function;
+ *   - return value: 0 = ok; > 0 = the cudaError_t of a failed runtime call; < 0 = argument error
+ *     (B200_ERR_* below) detected before anything was launched;
+ *   - "bf16" = 16-bit bfloat, "e4m3" = float8_e4m3fn bit patterns, "E8M0" = one byte b meaning 2^(b-127),
+ *     "E2M1" = 4-bit FP4 codes, two per byte, low nibble = even k (dsv41/quant.py:24-31, 98-103).
+ *
+ * The reference has no shared library for its GPU path: it launches cubin entry points through the driver API
+ * from Python (dsv41/cukern.py:24-57).  Each function below names the reference launcher(s) it replaces.
+ */
+#ifndef B200_MOE_H
+#define B200_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __DRIVER_TYPES_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+#define B200_ERR_BAD_ARG (-1)
+#define B200_ERR_BAD_SHAPE (-2)
+#define B200_ERR_BAD_ALIGN (-3)
+#define B200_ERR_WORKSPACE (-4)
+#define B200_ERR_UNSUPPORTED (-5)
+#define B200_ERR_TOO_LARGE (-6)
+
+/* weight / scale formats */
+#define B200_FMT_FP4_E8M0 0  /* E2M1 [.., N, K/2] + E8M0 byte per (row, 32 k)   : reference expert format   */
+#define B200_FMT_FP4_BF16S 1 /* E2M1 [.., N, K/2] + bf16 power-of-two per (row, 32 k)                         */
+#define B200_FMT_FP8_E8M0 2  /* e4m3 [N, K] + E8M0 byte per (32 rows, 32 k)      : reference dense format    */
+#define B200_FMT_FP8_F32B 3  /* e4m3 [N, K] + fp32 per (128 rows, 128 k), scale = blockmax/448                */
+
+/* router score functions (numbering of dsv41/fused2.py:497) */
+#define B200_SCORE_SQRTSOFTPLUS 0
+#define B200_SCORE_SIGMOID 1
+#define B200_SCORE_SOFTMAX 2
+
+int b200_version(void);
+/* host string for a return code of this library (never NULL) */
+const char* b200_error_string(int code);
+/* number of SMs of the current device as the persistent kernels size their grids */
+int b200_sm_count(void);
+
+/* ---- activation FP8 fake quantisation.  Replaces dsv41/fused.py:72-83 (fake_quant_fp8; spec dsv41/quant.py:46-54).
+ * x, y: bf16 [n_elems], n_elems % 32 == 0; groups of 32 along the flattened last dimension. */
+int b200_fake_quant_fp8(const void* x, void* y, long long n_elems, cudaStream_t stream);
+
+/* ---- router.  Replaces dsv41/fused2.py:486-502 (gate_topk; spec dsv41/model.py:1614-1630).
+ * scores fp32 [rows, n_experts]; bias fp32 [n_experts] or NULL; eid int32 [rows, topk]; wt fp32 [rows, topk].
+ * n_experts <= 1024, topk <= 32.  Equal keys select the lowest expert index. */
+int b200_gate_topk(const float* scores, const float* bias, int rows, int n_experts, float temp, int topk, float route_scale,
+                   int score_mode, int norm, int* eid, float* wt, cudaStream_t stream);
+
+/* ---- SwiGLU (+ routing weight) + per-32 FP8 fake quantisation.  Replaces dsv41/fused.py:309-316 (swiglu_quant).
+ * gu fp32 or bf16 [rows, 2*inter] (gate | up); weights fp32 [rows] or NULL; y bf16 [rows, inter]; inter % 32 == 0.
+ * permute != 0 stores the 8-k permuted layout of dsv41/fused.py:303-305. */
+int b200_swiglu_quant(const void* gu, int gu_is_bf16, const float* weights, long long rows, int inter, float limit, int permute, void* y,
+                      cudaStream_t stream);
+
+/* ---- routed + shared combine.  Replaces the NSUM branch of dsv41/fused2.py:518-523 and dsv41/model.py:2114-2118,2232.
+ * out[t, :] = bf16( sum_j y2[t*nsum + j, :] + ys[t, :] ); y2 fp32 [tokens*nsum, dim]; ys bf16 [tokens, dim] or NULL. */
+int b200_moe_combine(const float* y2, const void* ys, void* out, long long tokens, int nsum, int dim, cudaStream_t stream);
+
+/* ---- per-token partial row sums.  Replaces p2p_sum_rows (dsv41/cuda/p2p.cu:21-28, dsv41/cukern.py:370-379).
+ * dst[g*dst_stride + c] = sum_{r < rows} src[(g*rows + r)*n + c]; dst may be peer memory. */
+int b200_sum_rows(float* dst, const float* src, int rows, int n, int groups, long long dst_stride, cudaStream_t stream);
+
+/* ---- 8-k permuted copy of an activation.  Replaces dsv41/cukern.py:270-273 (permute_x).  bf16, n_elems % 8 == 0. */
+int b200_permute_x8(const void* x, void* y, long long n_elems, cudaStream_t stream);
+
+/* ---- grouped FP4 expert GEMM (decode form).  Replaces fp4_gemv_pairs (dsv41/cukern.py:60-77), fp4_gemv_m1
+ * (dsv41/cukern.py:286-306) and fp4_gemm_tc (dsv41/cukern.py:309-344); with accumulate != 0 it has the scatter-add
+ * contract of grouped_fp4_gemm (dsv41/moe_kernels.py:161-231).
+ *   out[pair_out[p], :] (+)= pair_w[p] * x[pair_tok[p], :] @ W[grp_expert[g] - shard_start]^T   for p in group g
+ *   x bf16 [rows, K] with row stride x_ld elements (x_perm8: the 8-k permuted layout); w uint8 [n, N, K/2],
+ *   s [n, N, K/32] (fmt B200_FMT_FP4_E8M0: bytes, B200_FMT_FP4_BF16S: bf16); w_estride / s_estride in BYTES;
+ *   grp_expert int32 [n_groups] (global ids, -1 = padding); group g owns pairs grp_start[g] .. +count-1 with count =
+ *   grp_count[g], or grp_start[g+1] - grp_start[g] when grp_count is NULL (then grp_start has n_groups+1 entries,
+ *   dsv41/decode.py:431-432; the grp_count form is the tile table of dsv41/moe_kernels.py:118-132); pair_tok / pair_out int32
+ *   [n_pairs] or NULL (= pair index); pair_w fp32 [n_pairs] or NULL; out fp32, row stride out_ld elements.
+ *   Groups whose expert is outside [shard_start, shard_start + shard_n) are skipped; with zero_out their rows are
+ *   zeroed (dsv41/cuda/fp4_tc.cu:66-72).  K % 128 == 0, N % 16 == 0, K <= 11264.  Groups of any size are accepted;
+ *   more than 8 pairs re-read the expert once per 8.
+ *   workspace: b200_fp4_grouped_workspace_bytes(n_pairs) bytes, 16-byte aligned. */
+size_t b200_fp4_grouped_workspace_bytes(int n_pairs);
+int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s, long long s_estride, int fmt,
+                          int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count, int n_groups, const int* pair_tok, const int* pair_out,
+                          const float* pair_w, int n_pairs, int shard_start, int shard_n, int zero_out, int accumulate, float* out, long long out_ld,
+                          void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
+/* ---- block-scaled FP8 dense GEMV / small-M GEMM.  Replaces fp8_gemv (dsv41/cukern.py:80-96), fp8_gemv_m1
+ * (dsv41/cukern.py:116-133) and fp8_gemm_tc (dsv41/cukern.py:165-221, group_cols = 0).
+ *   out[m, :] = x[m, :] @ dequant(w8, s)^T;  x bf16 [M, K] (row stride x_ld); w8 e4m3 [N, K];
+ *   fmt B200_FMT_FP8_E8M0: s uint8 [ceil(N/32), s_cols]; B200_FMT_FP8_F32B: s fp32 [ceil(N/128), s_cols];
+ *   w_permk != 0: weight bytes in the 16-k order of dsv41/w8.py:21-23 (what W8 holds);
+ *   out bf16 (out_is_f32 = 0) or fp32, row stride out_ld.  K % 64 == 0, N % 16 == 0, K <= 11264.  Any M; the weights
+ *   are read once per 8 rows. */
+int b200_fp8_gemm(const void* x, long long x_ld, int M, const void* w8, const void* s, int fmt, int s_cols, int w_permk, int N, int K, void* out,
+                  int out_is_f32, long long out_ld, cudaStream_t stream);
+
+/* ---- whole MoE layer for a decode batch: router -> input fake quantisation -> routed FP4 experts (gate/up, SwiGLU
+ * with routing weight, FP8 fake quantisation, down) -> shared FP8 expert -> combine.  Replaces, in one call, the
+ * chain dsv41/decode.py:446-464 (moe2 + experts_tc) + dsv41/fused2.py:518-523 and its fused single-token form
+ * cukern.expert_chain (dsv41/cukern.py:504-547); with a shard it is EPRuntime._experts_shard (dsv41/ep.py:324-338). */
+typedef struct b200_moe_args {
+    int tokens, n_experts, topk, dim, inter;
+    /* router: logits [tokens, n_experts] fp32 (logits_is_bf16 = 0) or bf16; bias fp32 [n_experts] or NULL */
+    const void* logits;
+    int logits_is_bf16;
+    const float* gate_bias;
+    float temp, route_scale;
+    int score_mode, norm;
+    /* input activation bf16 [tokens, dim]; x_is_quantized != 0 skips the per-32 FP8 fake quantisation */
+    const void* x;
+    int x_is_quantized;
+    /* routed experts of this shard: w13 [shard_n, 2*inter, dim/2], s13 [shard_n, 2*inter, dim/32],
+     * w2 [shard_n, dim, inter/2], s2 [shard_n, dim, inter/32]  (dsv41/load.py:213-249); expert_fmt = FP4_E8M0 or FP4_BF16S */
+    const void *w13, *s13, *w2, *s2;
+    int expert_fmt;
+    int shard_start, shard_n;
+    /* shared expert (FP8): sh_w13 e4m3 [2*inter, dim], sh_w2 e4m3 [dim, inter]; shared_fmt = FP8_E8M0 or FP8_F32B */
+    int has_shared;
+    const void *sh_w13, *sh_s13, *sh_w2, *sh_s2;
+    int shared_fmt, sh_s13_cols, sh_s2_cols, sh_permk;
+    float swiglu_limit;
+    /* outputs: out bf16 [tokens, dim] (may be NULL); routed_out fp32 [tokens, dim] = this shard's routed sum without
+     * the shared expert (may be NULL); eid_out int32 / wt_out fp32 [tokens, topk] (may be NULL) */
+    void* out;
+    float* routed_out;
+    int* eid_out;
+    float* wt_out;
+    void* workspace;
+    size_t workspace_bytes;
+} b200_moe_args;
+
+size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);
+int b200_moe_forward(const b200_moe_args* args, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MOE_H */

@@ -1,0 +1,227 @@
+"""Parity of every CUDA operator with the CPU oracle, through the C-ABI (the Python modules only marshal pointers).
+Sizes are chosen so the scalar oracle finishes in seconds.  Tolerances are the reference's own (dsv41/test_kernels.py:18-19,
+dsv41/test_fused.py:81-88, dsv41/test_fused2_units.py:69-75)."""
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16)
+
+
+def test_fake_quant_fp8_exact(mods, oracle, dev):
+    torch.manual_seed(0)
+    x = (torch.randn(3, 7, 4096) * 4).to(torch.bfloat16)
+    x[0, 0, :32] = 0
+    x[0, 1, :64] *= 1e-6
+    x[0, 2, :64] *= 3000
+    x[1, 0, 5] = 448 * 4
+    y = mods.fused.fake_quant_fp8(x.to(dev), 32).cpu()
+    ref = oracle.fake_quant_fp8(x, 32)
+    assert torch.equal(_bits(y), _bits(ref))
+    y2 = mods.quant.fake_quant_fp8(x.to(dev), 32).cpu()
+    assert torch.equal(_bits(y2), _bits(ref))
+
+
+@pytest.mark.parametrize("score_func", ["sqrtsoftplus", "sigmoid", "softmax"])
+@pytest.mark.parametrize("B,E,topk", [(1, 384, 6), (5, 384, 6), (64, 384, 6), (3, 8, 2), (2, 1000, 8)])
+def test_gate_topk(mods, oracle, dev, score_func, B, E, topk):
+    g = torch.Generator().manual_seed(B * 1000 + E)
+    sc = torch.randn(B, E, generator=g) * 2
+    bias = torch.randn(E, generator=g) * 0.1
+    e_ref, w_ref = oracle.gate_topk(sc, bias, 1.3, topk, 2.5, score_func, True)
+    eid, wt = mods.fused2.gate_topk(sc.to(dev), bias.to(dev), 1.3, topk, 2.5, score_func, True)
+    if B == 1:
+        assert eid.shape == (topk,) and wt.shape == (topk,)
+        eid, wt = eid.view(1, -1), wt.view(1, -1)
+    assert torch.equal(eid.cpu(), e_ref)
+    assert torch.allclose(wt.cpu(), w_ref, rtol=2e-5, atol=1e-9)
+    # no renormalisation, no bias, preallocated outputs
+    e_ref, w_ref = oracle.gate_topk(sc, None, 1.0, topk, 1.0, score_func, False)
+    eo = torch.empty(B, topk, dtype=torch.int32, device=dev)
+    wo = torch.empty(B, topk, dtype=torch.float32, device=dev)
+    mods.fused2.gate_topk(sc.to(dev), None, 1.0, topk, 1.0, score_func, False, eid=eo, wt=wo)
+    assert torch.equal(eo.cpu(), e_ref) and torch.allclose(wo.cpu(), w_ref, rtol=2e-5, atol=1e-9)
+
+
+def test_gate_topk_tie_lowest_index(mods, dev):
+    sc = torch.zeros(2, 384)
+    sc[1, 100:110] = 1.0
+    eid, _ = mods.fused2.gate_topk(sc.to(dev), torch.zeros(384, device=dev), 1.0, 6, 1.0, "softmax", True)
+    assert eid.cpu().tolist() == [[0, 1, 2, 3, 4, 5], [100, 101, 102, 103, 104, 105]]
+
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("limit", [10.0, 0.0])
+def test_swiglu_quant(mods, oracle, dev, in_dtype, limit):
+    torch.manual_seed(1)
+    inter = 2304
+    gu = (torch.randn(9, 2 * inter) * 5).to(in_dtype)
+    wt = torch.rand(9)
+    for w in (wt, None):
+        ref = oracle.swiglu_quant(gu.float(), w, inter, limit)
+        y = mods.fused.swiglu_quant(gu.to(dev), w.to(dev) if w is not None else None, inter, limit).cpu()
+        same = (_bits(y) == _bits(ref)).float().mean().item()
+        assert same >= 0.999, same  # expf rounding may flip a bf16 boundary on isolated elements
+        assert (y.float() - ref.float()).abs().max().item() <= 0.07 * ref.float().abs().max().item()
+    yp = mods.fused.swiglu_quant(gu.to(dev), wt.to(dev), inter, limit, permute=True)
+    y0 = mods.fused.swiglu_quant(gu.to(dev), wt.to(dev), inter, limit)
+    assert torch.equal(yp, mods.cukern.permute_x(y0))
+
+
+def test_permute_x(mods, dev):
+    x = torch.arange(64, dtype=torch.float32).view(2, 32).to(torch.bfloat16)
+    y = mods.cukern.permute_x(x.to(dev)).cpu()
+    ref = x.view(2, 4, 8)[:, :, [0, 4, 2, 6, 1, 5, 3, 7]].reshape(2, 32)
+    assert torch.equal(y, ref)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2304, 5120), (7, 5120, 2304), (64, 2304, 5120), (20, 4096, 2048), (3, 64, 128), (9, 48, 512)])
+def test_fp4_gemm(mods, oracle, dev, M, N, K):
+    g = torch.Generator().manual_seed(M + N + K)
+    w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    s = torch.randint(110, 135, (N, K // 32), dtype=torch.uint8, generator=g)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    ref = oracle.fp4_gemm(a, w, s)
+    out = mods.kernels.fp4_gemm(a.to(dev), w.to(dev), s.to(dev))
+    assert out.dtype == torch.float32 and out.shape == (M, N)
+    assert rel_err(out, ref) < 2e-3
+
+
+def test_fp4_scale_byte_zero_and_bf16_scales(mods, oracle, dev):
+    g = torch.Generator().manual_seed(5)
+    N, K, M = 64, 512, 3
+    w = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g)
+    s = torch.randint(120, 130, (N, K // 32), dtype=torch.uint8, generator=g)
+    s[::3, ::2] = 0  # byte 0 decodes to 0 (dsv41/cpu/moe_cpu.cpp:190)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    ref = oracle.fp4_gemm(a, w, s)
+    out = mods.kernels.fp4_gemm(a.to(dev), w.to(dev), s.to(dev))
+    assert rel_err(out, ref) < 2e-3
+    s2 = torch.randint(120, 130, (N, K // 32), dtype=torch.uint8, generator=g)
+    ref2 = oracle.fp4_gemm(a, w, s2)
+    ge = torch.zeros(1, dtype=torch.int32, device=dev)
+    gs = torch.tensor([0, M], dtype=torch.int32, device=dev)
+    out2 = mods.cukern.grouped_fp4(a.to(dev), w.to(dev).unsqueeze(0), mods.synth.e8m0_to_bf16(s2).to(dev).unsqueeze(0), ge, gs, None, None, None, None, M)
+    assert rel_err(out2, ref2) < 2e-3
+
+
+def _experts(E, N, K, seed, lo=110, hi=135):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, 256, (E, N, K // 2), dtype=torch.uint8, generator=g), torch.randint(lo, hi, (E, N, K // 32), dtype=torch.uint8, generator=g), g)
+
+
+def test_fp4_gemv_pairs(mods, oracle, dev):
+    E, N, K = 6, 512, 1024
+    w, s, g = _experts(E, N, K, 11)
+    x = torch.randn(4, K, generator=g).to(torch.bfloat16)
+    P = 13
+    row_in = torch.randint(0, 4, (P,), generator=g, dtype=torch.int32)
+    expert = torch.randint(0, E, (P,), generator=g, dtype=torch.int32)
+    wt = torch.rand(P, generator=g)
+    ref = oracle.fp4_pairs(x, w, s, expert, row_in, torch.arange(P), wt, P)
+    out = mods.cukern.fp4_gemv_pairs(x.to(dev), w.to(dev), s.to(dev), row_in.to(dev), expert.to(dev), wt.to(dev), P)
+    assert rel_err(out, ref) < 2e-3
+
+
+@pytest.mark.parametrize("G,M", [(1, 1), (1, 8), (1, 16), (6, 1), (6, 4), (3, 21)])
+def test_fp4_gemm_tc_groups_and_shards(mods, oracle, dev, G, M):
+    """Grouped form of dsv41/test_fp4_tc.py:31-41 plus the shard rule: foreign groups are skipped, zero_out zeroes their rows."""
+    E, N, K = 8, 256, 1024
+    w, s, g = _experts(E, N, K, 100 + G * 10 + M, 112, 128)
+    x = mods.quant.fake_quant_fp8((torch.randn(M, K, generator=g) * 2).to(torch.bfloat16), 32)
+    xp = mods.cukern.permute_x(x.to(dev))
+    experts = torch.arange(G, dtype=torch.int32)
+    grp_start = torch.arange(0, G * M + 1, M, dtype=torch.int32)
+    pair_tok = torch.arange(M, dtype=torch.int32).repeat(G)
+    P = G * M
+    ref = oracle.fp4_pairs(x, w, s, experts.repeat_interleave(M), pair_tok, torch.arange(P), None, P)
+    y = mods.cukern.fp4_gemm_tc(xp, w.to(dev), s.to(dev), experts.to(dev), grp_start.to(dev), pair_tok.to(dev), P, M)
+    assert rel_err(y, ref) < 2e-3
+    if G > 1:  # this GPU holds experts [2, 5): local tensors are w[2:5]
+        out = torch.full((P, N), 7.0, device=dev)
+        y = mods.cukern.fp4_gemm_tc(xp, w[2:5].to(dev), s[2:5].to(dev), experts.to(dev), grp_start.to(dev), pair_tok.to(dev), P, M, shard_start=2, shard_n=3,
+                                    zero_out=True, out=out)
+        mask = ((experts >= 2) & (experts < 5)).repeat_interleave(M)
+        ref_sh = ref * mask[:, None]
+        assert rel_err(y, ref_sh) < 2e-3
+        assert (y.cpu()[~mask] == 0).all()
+        out = torch.full((P, N), 7.0, device=dev)
+        y = mods.cukern.fp4_gemm_tc(xp, w[2:5].to(dev), s[2:5].to(dev), experts.to(dev), grp_start.to(dev), pair_tok.to(dev), P, M, shard_start=2, shard_n=3,
+                                    zero_out=False, out=out)
+        assert (y.cpu()[~mask] == 7.0).all()
+
+
+@pytest.mark.parametrize("M,topk", [(1, 6), (5, 6), (64, 6), (100, 6)])
+def test_grouped_fp4_gemm_scatter_add(mods, oracle, dev, M, topk):
+    """dsv41/test_moe.py:21-36 at reduced size: out[row_out] += weight * a[row_in] @ W[expert]^T."""
+    E, N, K = 16, 256, 512
+    w, s, g = _experts(E, N, K, 200 + M)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    eid = torch.randint(0, E, (M, topk), generator=g)
+    wt = torch.rand(M, topk, generator=g)
+    row_in = torch.arange(M).repeat_interleave(topk)
+    ref = oracle.fp4_pairs(a, w, s, eid.flatten(), row_in, row_in, wt.flatten(), M)
+    pairs = mods.moe_kernels.GroupedPairs(eid.flatten().to(dev), row_in.to(dev), row_in.clone().to(dev), wt.flatten().to(dev), block_m=16 if M <= 16 else 64,
+                                          n_experts=E)
+    out = mods.moe_kernels.grouped_fp4_gemm(a.to(dev), w.to(dev), s.to(dev), pairs, M)
+    assert rel_err(out, ref) < 2e-3
+    out2 = mods.moe_kernels.grouped_fp4_gemm_chunked(a.to(dev), w.to(dev), s.to(dev), pairs, M, chunk_rows=32)
+    assert rel_err(out2, ref) < 2e-3
+
+
+def _rand_fp8(N, K, g, lo=110, hi=130):
+    w = torch.randint(0, 256, (N, K), dtype=torch.uint8, generator=g)
+    w[(w & 0x7F) == 0x7F] = 0  # no NaN codes (dsv41/test_fp8_tc.py:12-16)
+    s = torch.randint(lo, hi, ((N + 31) // 32, K // 32), dtype=torch.uint8, generator=g)
+    return w, s
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 5120), (1, 1280, 5120), (6, 5120, 8192), (16, 4608, 5120), (1, 5120, 2304), (3, 4096, 1280), (8, 64, 64)])
+def test_fp8_gemm_e8m0(mods, oracle, dev, M, N, K):
+    g = torch.Generator().manual_seed(N + K + M)
+    w, s = _rand_fp8(N, K, g)
+    x = mods.quant.fake_quant_fp8((torch.randn(M, K, generator=g) * 2).to(torch.bfloat16), 32)
+    ref = oracle.fp8_gemm(x, w, s)
+    y = mods.cukern.fp8_gemm_tc(x.to(dev), mods.w8.permute_k(w).to(dev), s.to(dev), out_dtype=torch.float32)
+    assert rel_err(y, ref) < 2e-3
+    yb = mods.cukern.fp8_gemm_tc(x.to(dev), mods.w8.permute_k(w).to(dev), s.to(dev))
+    assert yb.dtype == torch.bfloat16 and rel_err(yb, ref) < 1e-2
+    if M == 1:
+        y1 = mods.cukern.fp8_gemv(x.to(dev), w.to(dev), s.to(dev))
+        assert y1.dtype == torch.float32 and rel_err(y1, ref) < 2e-3
+        y2 = mods.cukern.fp8_gemv_m1(x.to(dev), mods.w8.permute_k(w).to(dev), s.to(dev))
+        assert y2.dtype == torch.bfloat16 and rel_err(y2, ref) < 1e-2
+    W = mods.w8.W8(w.to(dev), s.to(dev))
+    yl = mods.w8.linear_w(x.to(dev), W)
+    assert rel_err(yl, ref) < 1e-2
+    assert rel_err(yl, torch.nn.functional.linear(x.to(dev), W.bf16())) < 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("N", [4096, 12288])
+def test_fp8_gemv_f32_block_scales(mods, oracle, dev, M, N):
+    """The 128x128 fp32-scaled format: weights N(0, 0.02) quantised per block with scale = blockmax/448."""
+    K = 4096
+    g = torch.Generator().manual_seed(N + M)
+    wf = torch.randn(N, K, generator=g) * 0.02
+    codes, scale = mods.synth.quantize_fp8_block(wf, "f32b")
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    ref = oracle.fp8_gemm(x, codes, scale)
+    y = mods.cukern.fp8_gemm_tc(x.to(dev), codes.to(dev), scale.to(dev), out_dtype=torch.float32, permuted=False)
+    assert rel_err(y, ref) < 2e-3
+    # the quantised matrix stays close to the fp32 one
+    assert rel_err(ref, x.float() @ wf.T) < 0.1
+    W = mods.w8.W8(codes.to(dev), scale.to(dev))
+    assert rel_err(mods.w8.linear_w(x.to(dev), W), ref) < 1e-2
+
+
+def test_p2p_sum_rows(mods, dev):
+    src = torch.randn(3 * 6, 500, device=dev)
+    dst = torch.zeros(3, 512, device=dev)
+    mods.cukern.p2p_sum_rows(dst, src, dev, groups=3)
+    assert torch.allclose(dst[:, :500], src.view(3, 6, 500).sum(1), atol=1e-5)
