@@ -1,0 +1,372 @@
+"""Benchmark of the MoE-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode64|decode32|decode8|decode1] [--impl reference]
+    torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W      (N > 1: expert parallel)
+
+A step = one pass of the whole MoE layer (router -> input FP8 fake quantisation -> routed FP4 experts -> FP8 shared
+expert -> combine) over one batch of synthetic tokens.  Layer shapes: 384 experts, hidden 4096, expert width 2048,
+top-6 + 1 shared expert; all 384 experts resident (N = 1) or range-sharded 384/N per GPU (N > 1).
+
+Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; `e2e` = the same through the public API
+with pinned HOST buffers (host->device and device->host copies inside the timed region); `roofline` = the dominant kernel
+(the routed gate/up weight stream) timed live with CUDA events against the measured HBM peak; `cpu_baseline` = the
+reference's own CPU expert chain timed on this box's host cores (N = 1 only).
+`--impl reference` times only that CPU implementation, on the same workload and metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+E, D, I, TOPK = 384, 4096, 2048, 6
+WORKLOADS = {"decode64": 64, "decode32": 32, "decode8": 8, "decode1": 1}
+POOL = 12             # distinct (tokens, logits) sets cycled over the steps
+ROTATE = 29           # expert-id shift of the Zipf ranking between consecutive sets: hot experts change every step
+SEED = 1234
+METRIC = "MoE-layer tok/s (decode S=1..64, prefill 4K) at 1/2/4/8 B200; % HBM/TC roofline"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            j = json.load(open(p))
+            return float(j["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+    Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.path = index, None, f"/tmp/b200_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def dist_env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), world
+
+
+# ----------------------------------------------------------------------------------------------------------------- CPU arm
+def cpu_experts(n: int, seed: int):
+    from __graft_entry__ import _import
+    return _import("synth").make_experts(n, D, I, seed=seed)
+
+
+def time_cpu_chain(tokens_per_step: int, steps: int, warmup: int, budget_s: float, n_resident: int = 48):
+    """The reference's CPU implementation of the path: routed expert chain of one token at a time (the library does not
+    batch), 6 experts per token, expert ids rotated so the weights stream from DRAM (method of dsv41/test_cpumoe.py:32-35).
+    Returns (tokens/s, description dict).  Uses oracle/_ref (the reference's own C++ compiled from its sources) when the
+    host CPU can run it, else this repository's C port."""
+    from oracle import oracle as O
+    from __graft_entry__ import _import
+    synth = _import("synth")
+    ex = cpu_experts(n_resident, SEED + 99)
+    x = O.fake_quant_fp8(synth.make_tokens(1, D, SEED + 5), 32)[0]
+    wts = [0.3, 0.2, 0.15, 0.15, 0.1, 0.1]
+    kind, cores, mode_note = "port", os.cpu_count() or 1, ""
+    ref = None
+    try:
+        ref = O.RefCpuMoe(int8_mode=2)  # the reference's production default (dsv41/cpumoe.py:36)
+        kind, cores, mode_note = "reference", ref.threads, "int8 mode 2 (its default); "
+    except Exception as e:  # no AVX-512 BF16 on this host, or library not built
+        mode_note = f"C port ({type(e).__name__}); "
+    import ctypes
+
+    def one_token(i: int):
+        ids = [(e * 7 + 6 * i) % n_resident for e in range(6)]
+        if ref is not None:
+            ref.forward(x, ex["w13"], ex["s13"], ex["w2"], ex["s2"], ids, wts, 10.0)
+        else:
+            P = ctypes.c_void_p * 6
+            out = torch.empty(D)
+            O.lib().orc_routed_token(P(*[ex["w13"][e].data_ptr() for e in ids]), P(*[ex["s13"][e].data_ptr() for e in ids]),
+                                     P(*[ex["w2"][e].data_ptr() for e in ids]), P(*[ex["s2"][e].data_ptr() for e in ids]), 6,
+                                     ctypes.c_void_p(x.data_ptr()), (ctypes.c_float * 6)(*wts), ctypes.c_void_p(out.data_ptr()), D, I, D, ctypes.c_float(10.0))
+
+    n = 0
+    for _ in range(max(1, warmup)):
+        one_token(n)
+        n += 1
+    t0 = time.perf_counter()
+    done_steps, done_tokens = 0, 0
+    while done_steps < steps:
+        for _ in range(tokens_per_step):
+            one_token(n)
+            n += 1
+            done_tokens += 1
+            if time.perf_counter() - t0 > budget_s:
+                break
+        else:
+            done_steps += 1
+            continue
+        break
+    dt = time.perf_counter() - t0
+    tps = done_tokens / dt
+    desc = {"kind": kind, "cores": cores,
+            "sample": f"{mode_note}routed expert chain only (no router, no shared expert), one token per call, {done_tokens} tokens x 6 experts, "
+                      f"ids rotated over {n_resident} resident experts, {dt:.1f} s"}
+    return tps, dt, done_tokens, desc
+
+
+def run_reference(args):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    S = WORKLOADS[args.workload]
+    tps, dt, done, desc = time_cpu_chain(S, args.steps, args.warmup, budget_s=120.0)
+    steps_done = max(1, done // S)
+    line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * dt / max(done / S, 1e-9), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args.workload, args.gpus),
+            "cpu_baseline": dict(value=tps, unit="tokens/s", **desc),
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "steps_completed": steps_done}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name: str, gpus: int) -> dict:
+    S = WORKLOADS[name]
+    return {"workload": f"moe_{name}: {S} decode tokens, 384 experts (FP4 e2m1 + E8M0/32), hidden 4096, inter 2048, top-6 Zipf(s=1) softmax routing, "
+                        f"+1 FP8 (e4m3 + E8M0 32x32) shared expert", "tokens": S, "experts": E, "hidden": D, "inter": I, "topk": TOPK,
+            "parallelism": "single GPU, all experts resident" if gpus == 1 else f"ep{gpus}: experts sharded {E // gpus}/GPU, tokens split {S}/{gpus}",
+            "l2": f"inputs larger than L2: {POOL} token/logit sets cycle, Zipf ranking rotated by {ROTATE} experts per set over 5.13 GB of experts"}
+
+
+# ----------------------------------------------------------------------------------------------------------------- GPU arm
+def build_inputs(synth, S: int, dev):
+    xs, ls = [], []
+    for i in range(POOL):
+        xs.append(synth.make_tokens(S, D, SEED + 10 + i))
+        ls.append(synth.make_logits(S, E, SEED + 3, topk=TOPK, rotate=ROTATE * i))
+    return xs, ls
+
+
+def time_steps(fn, steps: int, warmup: int, barrier):
+    for i in range(warmup):
+        fn(i)
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / steps  # ms per step
+
+
+def run_gpu(args):
+    import __graft_entry__ as g
+    rank, local_rank, world = dist_env()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    g.load_package()
+    synth, moe, w8, ep = g._import("synth"), g._import("moe"), g._import("w8"), g._import("ep")
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    S = WORKLOADS[args.workload]
+    start, n_local = ep.shard_ranges(E, world)[rank]
+    # identical expert bits on every rank: the full layer is generated on the device from one seed, the rank keeps its slice
+    ex = synth.make_experts(E, D, I, seed=SEED, device=dev)
+    if world > 1:
+        ex = {k: v[start:start + n_local].clone() for k, v in ex.items()}
+        torch.cuda.empty_cache()
+    sh = synth.make_shared(D, I, seed=SEED + 1, kind="e8m0", device=dev)
+    layer = moe.MoELayer(ex["w13"], ex["s13"], ex["w2"], ex["s2"], n_experts=E, topk=TOPK, sh_w13=w8.W8(sh["w13"], sh["s13"]), sh_w2=w8.W8(sh["w2"], sh["s2"]),
+                         swiglu_limit=10.0, shard_start=start)
+    xs_h, ls_h = build_inputs(synth, S, dev)
+    counts = [c for _, c in ep.split_tokens(S, world)]
+    first = sum(counts[:rank])
+    T_r = counts[rank]
+    xs = [x[first:first + T_r].to(dev) for x in xs_h]
+    ls = [l[first:first + T_r].to(dev) for l in ls_h]
+    out = torch.empty(T_r, D, device=dev, dtype=torch.bfloat16)
+    epl = ep.EPMoE(layer) if world > 1 else None
+
+    # unique experts touched per input set (bookkeeping for the byte counts; untimed)
+    uniq = []
+    for i in range(POOL):
+        _, eid, _ = layer.forward(xs_h[i].to(dev), ls_h[i].to(dev), want_route=True)
+        uniq.append(int(torch.unique(eid).numel()))
+    torch.cuda.synchronize()
+
+    # ---- value: inputs resident in HBM
+    prof = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps + args.warmup)]
+    for a, b in prof:
+        a.record()
+        b.record()
+    torch.cuda.synchronize()
+
+    def step_resident(i):
+        j = i % POOL
+        if world == 1:
+            layer.forward(xs[j], ls[j], out=out, prof_events=prof[i])
+        else:
+            out.copy_(epl.forward(xs[j], ls[j], counts))
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms = max_over_ranks(time_steps(step_resident, args.steps, args.warmup, barrier))
+    clocks = sampler.stop() if rank == 0 else {}
+    value = S / (ms * 1e-3)
+
+    # ---- e2e: host buffers, copies inside the timed region
+    xh = [x[first:first + T_r].contiguous().pin_memory() for x in xs_h]
+    lh = [l[first:first + T_r].contiguous().pin_memory() for l in ls_h]
+    oh = torch.empty(T_r, D, dtype=torch.bfloat16).pin_memory()
+    xd, ld = torch.empty_like(xs[0]), torch.empty_like(ls[0])
+
+    def step_e2e(i):
+        j = i % POOL
+        xd.copy_(xh[j], non_blocking=True)
+        ld.copy_(lh[j], non_blocking=True)
+        if world == 1:
+            layer.forward(xd, ld, out=out)
+        else:
+            out.copy_(epl.forward(xd, ld, counts))
+        oh.copy_(out, non_blocking=True)
+
+    ms_e2e = max_over_ranks(time_steps(step_e2e, args.steps, args.warmup, barrier))
+    h2d = T_r * (D * 2 + E * 2) * world
+    d2h = T_r * D * 2 * world
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_peaks()
+    exp_b13 = 2 * I * D // 2 + 2 * I * D // 32
+    line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(args.workload, world), "clocks": clocks,
+            "e2e": {"value": S / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
+            "gpu_launches": (6 if world == 1 else 9) * args.steps}
+    if world == 1:
+        durs = [prof[args.warmup + i][0].elapsed_time(prof[args.warmup + i][1]) for i in range(args.steps)]
+        u_steps = [uniq[(args.warmup + i) % POOL] for i in range(args.steps)]
+        alg = statistics.mean(u_steps) * exp_b13
+        avg_ms = statistics.mean(durs)
+        achieved = alg / (avg_ms * 1e-3) / 1e9
+        layer_bytes = statistics.mean(u_steps) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                            "kernel": "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)",
+                            "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
+                            "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": statistics.mean(u_steps),
+                            "whole_layer": {"bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
+                                            "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak}}
+        # other decode batch sizes of the same configuration (short runs, same method)
+        sweep = {}
+        if not args.no_sweep:
+            for name, s2 in WORKLOADS.items():
+                if name == args.workload:
+                    continue
+                xs2, ls2 = build_inputs(synth, s2, dev)
+                xs2, ls2 = [x.to(dev) for x in xs2], [l.to(dev) for l in ls2]
+                o2 = torch.empty(s2, D, device=dev, dtype=torch.bfloat16)
+                u2 = []
+                for i in range(POOL):
+                    _, eid, _ = layer.forward(xs2[i], ls2[i], want_route=True)
+                    u2.append(int(torch.unique(eid).numel()))
+                m2 = time_steps(lambda i: layer.forward(xs2[i % POOL], ls2[i % POOL], out=o2), args.steps, args.warmup, barrier)
+                b2 = statistics.mean(u2) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
+                sweep[name] = {"tokens_per_s": s2 / (m2 * 1e-3), "ms_per_step": m2, "unique_experts": statistics.mean(u2), "layer_gbs": b2 / (m2 * 1e-3) / 1e9,
+                               "layer_hbm_frac": b2 / (m2 * 1e-3) / 1e9 / peak}
+        line["sweep"] = sweep
+        if not args.no_cpu:
+            tps, dt, done, desc = time_cpu_chain(S, 10 ** 9, 1, budget_s=args.cpu_seconds)
+            line["cpu_baseline"] = dict(value=tps, unit="tokens/s", **desc)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -315,8 +315,10 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = D;
     a.work = work; a.n_work = n_work; a.pair_tok = pair_tok; a.pair_out = nullptr; a.pair_w = pair_w;
     a.out = hq; a.out_ld = I; a.limit = m->swiglu_limit; a.inter = I;
+    if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
     int rc = skinny_launch(a, m->expert_fmt, SK_EPI_SWIGLU, stream);
     if (rc) return rc;
+    if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
     // routed down -> y2 [original pair, dim] fp32
     SkinnyArgs b{};
     b.w = (const uint8_t*)m->w2; b.w_estride = (long long)D * (I / 2);

@@ -37,10 +37,10 @@ class MoELayer:
         self.device = dev
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, *, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
-                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True):
+                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, prof_events=None):
         """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E].
         Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
-        and (eid, wt)."""
+        and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel."""
         dev = L.require_cuda(x, logits, out)
         assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.is_contiguous()
         T = x.shape[0]
@@ -74,6 +74,8 @@ class MoELayer:
         a.eid_out = eid.data_ptr() if eid is not None else None
         a.wt_out = wt.data_ptr() if wt is not None else None
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        if prof_events is not None:  # (start, stop) torch.cuda.Event pair, already created (recorded once), timing enabled
+            a.prof_start, a.prof_stop = prof_events[0].cuda_event, prof_events[1].cuda_event
         with torch.cuda.device(dev):
             L.check(lib.b200_moe_forward(ctypes.byref(a), L.stream_of(dev)), "b200_moe_forward")
         res = [out] if final else []

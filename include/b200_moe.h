@@ -143,6 +143,10 @@ typedef struct b200_moe_args {
     float* wt_out;
     void* workspace;
     size_t workspace_bytes;
+    /* optional cudaEvent_t pair recorded on `stream` right before and after the dominant kernel of the layer (the routed
+     * gate/up weight stream), so that a benchmark can time that kernel alone; NULL = not recorded */
+    void* prof_start;
+    void* prof_stop;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);
