@@ -43,7 +43,7 @@ _SIGNATURES = {
     "b200_sum_rows": (c_i, [c_p, c_p, c_i, c_i, c_i, c_ll, c_p]),
     "b200_permute_x8": (c_i, [c_p, c_p, c_ll, c_p]),
     "b200_fp4_grouped_workspace_bytes": (c_sz, [c_i]),
-    "b200_fp4_grouped_gemm": (c_i, [c_p, c_ll, c_i, c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i,
+    "b200_fp4_grouped_gemm": (c_i, [c_p, c_ll, c_i, c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i,
                                     c_p, c_ll, c_p, c_sz, c_p]),
     "b200_fp8_gemm": (c_i, [c_p, c_ll, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_ll, c_p]),
     "b200_moe_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),

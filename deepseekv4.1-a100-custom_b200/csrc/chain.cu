@@ -33,9 +33,9 @@ struct RouteArgs {
     unsigned int* counter;
 };
 
-// One block per token: fake-quantise the token's activation (dsv41/quant.py:46-54) and route it (dsv41/model.py:1614-1630).
-// The last block to finish buckets all pairs by expert (stable, the order of dsv41/moe_kernels.py:111-116 and
-// dsv41/decode.py:417-433) and emits the work list of the shard's experts.
+// One block per token: fake-quantise the token's activation (dsv41/quant.py:46-54; one thread per group of 32, four 16-byte
+// loads in flight) and route it (dsv41/model.py:1614-1630).  The last block to finish buckets all pairs by expert (stable, the
+// order of dsv41/moe_kernels.py:111-116 and dsv41/decode.py:417-433) and emits the work list of the shard's experts.
 __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArgs a) {
     __shared__ float sh_f[8];
     __shared__ int sh_i[4];
@@ -44,16 +44,32 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
     __shared__ int s_cnt[ROUTE_MAX_EXPERTS];
     __shared__ int s_start[ROUTE_MAX_EXPERTS];
     __shared__ int s_woff[ROUTE_MAX_EXPERTS];
-    __shared__ int s_scan[ROUTE_THREADS];
+    __shared__ int s_wtot[2][ROUTE_THREADS / 32];
     const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     if (a.xq) {
         const int groups = a.dim >> 5;
-        for (int gi = warp; gi < groups; gi += ROUTE_THREADS / 32) {
-            const long off = (long)tok * a.dim + gi * 32 + lane;
-            const float v = __bfloat162float(a.x[off]);
-            const float s = fp8_group_scale(warp_max(fabsf(v)));
-            a.xq[off] = __float2bfloat16_rn(fp8_fake_quant_value(v, s));
+        for (int gi = tid; gi < groups; gi += ROUTE_THREADS) {
+            const uint4* src = reinterpret_cast<const uint4*>(a.x + (long)tok * a.dim + gi * 32);
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = src[j];
+            const uint32_t* w = reinterpret_cast<const uint32_t*>(v);
+            float f[32], amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                f[2 * j] = bf16_bits_to_f32(w[j] & 0xFFFFu);
+                f[2 * j + 1] = bf16_bits_to_f32(w[j] >> 16);
+                amax = fmaxf(amax, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
+            }
+            const float s = fp8_group_scale(amax);
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                o[j] = f32_to_bf16_bits(fp8_fake_quant_value(f[2 * j], s)) | (f32_to_bf16_bits(fp8_fake_quant_value(f[2 * j + 1], s)) << 16);
+            uint4* dst = reinterpret_cast<uint4*>(a.xq + (long)tok * a.dim + gi * 32);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
     }
     gate_topk_row(a.logits_f32 ? a.logits_f32 + (long)tok * a.E : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.E : nullptr, a.bias, a.E,
@@ -74,52 +90,61 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
         atomicAdd(&s_cnt[e], 1);
     }
     __syncthreads();
-    // exclusive scans over experts: pair offsets (all experts) and work offsets (this shard's experts)
+    // exclusive scans over experts: pair offsets (all experts) and work offsets (this shard's experts); thread t owns the
+    // experts [t*per, t*per + per)
     const int per = (E + ROUTE_THREADS - 1) / ROUTE_THREADS;
-    for (int pass = 0; pass < 2; ++pass) {
-        int local = 0;
-        for (int i = 0; i < per; ++i) {
-            const int e = tid * per + i;
-            if (e < E) {
-                const bool mine = e >= a.shard_start && e < a.shard_start + a.shard_n;
-                local += pass == 0 ? s_cnt[e] : (mine ? (s_cnt[e] + SK_TOK - 1) / SK_TOK : 0);
-            }
+    int loc_p = 0, loc_w = 0;
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < E) {
+            loc_p += s_cnt[e];
+            if (e >= a.shard_start && e < a.shard_start + a.shard_n) loc_w += (s_cnt[e] + SK_TOK - 1) / SK_TOK;
         }
-        s_scan[tid] = local;
-        __syncthreads();
-        if (tid == 0) {
-            int run = 0;
-            for (int i = 0; i < ROUTE_THREADS; ++i) { int v = s_scan[i]; s_scan[i] = run; run += v; }
-            if (pass == 1) *a.n_work = run;
-        }
-        __syncthreads();
-        int run = s_scan[tid];
-        for (int i = 0; i < per; ++i) {
-            const int e = tid * per + i;
-            if (e < E) {
-                const bool mine = e >= a.shard_start && e < a.shard_start + a.shard_n;
-                if (pass == 0) { s_start[e] = run; run += s_cnt[e]; }
-                else { s_woff[e] = run; run += mine ? (s_cnt[e] + SK_TOK - 1) / SK_TOK : 0; }
-            }
-        }
-        __syncthreads();
     }
-    // stable placement: the thread that owns expert e walks the pairs in index order
-    for (int e = tid; e < E; e += ROUTE_THREADS) {
+    int inc_p = loc_p, inc_w = loc_w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int vp = __shfl_up_sync(0xffffffffu, inc_p, o), vw = __shfl_up_sync(0xffffffffu, inc_w, o);
+        if (lane >= o) { inc_p += vp; inc_w += vw; }
+    }
+    if (lane == 31) { s_wtot[0][warp] = inc_p; s_wtot[1][warp] = inc_w; }
+    __syncthreads();
+    int run_p = inc_p - loc_p, run_w = inc_w - loc_w, tot_w = 0;
+    for (int w = 0; w < ROUTE_THREADS / 32; ++w) {
+        if (w < warp) { run_p += s_wtot[0][w]; run_w += s_wtot[1][w]; }
+        tot_w += s_wtot[1][w];
+    }
+    if (tid == 0) *a.n_work = tot_w;
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < E) {
+            s_start[e] = run_p;
+            s_woff[e] = run_w;
+            run_p += s_cnt[e];
+            if (e >= a.shard_start && e < a.shard_start + a.shard_n) run_w += (s_cnt[e] + SK_TOK - 1) / SK_TOK;
+        }
+    }
+    __syncthreads();
+    // stable placement: one warp per expert walks the pairs 32 at a time (ballot + prefix popcount keeps the pair order)
+    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
         const int cnt = s_cnt[e];
         if (cnt == 0) continue;
         int pos = s_start[e];
-        for (int p = 0; p < P; ++p) {
-            if (s_eid[p] == e) {
-                a.pair_tok[pos] = p / a.topk;
-                a.pair_out[pos] = p;
-                a.pair_w[pos] = __ldcg(a.wt + p);
-                ++pos;
+        for (int base = 0; base < P; base += 32) {
+            const int p = base + lane;
+            const bool hit = p < P && s_eid[p] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int o = pos + __popc(m & ((1u << lane) - 1u));
+                a.pair_tok[o] = p / a.topk;
+                a.pair_out[o] = p;
+                a.pair_w[o] = __ldcg(a.wt + p);
             }
+            pos += __popc(m);
         }
         if (e >= a.shard_start && e < a.shard_start + a.shard_n) {
             const int nsub = (cnt + SK_TOK - 1) / SK_TOK;
-            for (int i = 0; i < nsub; ++i) {
+            for (int i = lane; i < nsub; i += 32) {
                 const int rem = cnt - i * SK_TOK;
                 a.work[s_woff[e] + i] = make_int4(e - a.shard_start, s_start[e] + i * SK_TOK, rem < SK_TOK ? rem : SK_TOK, e);
             }
@@ -190,11 +215,11 @@ extern "C" size_t b200_fp4_grouped_workspace_bytes(int n_pairs) {
 }
 
 extern "C" int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s,
-                                     long long s_estride, int fmt, int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count,
-                                     int n_groups, const int* pair_tok, const int* pair_out, const float* pair_w, int n_pairs, int shard_start, int shard_n,
+                                     long long s_estride, int fmt, int n_local_experts, int N, int K, const int* grp_expert, const int* grp_start,
+                                     const int* grp_count, int n_groups, const int* pair_tok, const int* pair_out, const float* pair_w, int n_pairs, int shard_start, int shard_n,
                                      int zero_out, int accumulate, float* out, long long out_ld, void* workspace, size_t workspace_bytes,
                                      cudaStream_t stream) {
-    if (!x || !w || !s || !grp_expert || !grp_start || !out || !workspace || n_groups < 0 || n_pairs < 0) return ERR_BAD_ARG;
+    if (!x || !w || !s || !grp_expert || !grp_start || !out || !workspace || n_groups < 0 || n_pairs < 0 || n_local_experts < 1) return ERR_BAD_ARG;
     if (fmt != SK_FMT_FP4_E8M0 && fmt != SK_FMT_FP4_BF16S) return ERR_UNSUPPORTED;
     if (workspace_bytes < b200_fp4_grouped_workspace_bytes(n_pairs) || ((uintptr_t)workspace & 15)) return ERR_WORKSPACE;
     if (n_pairs == 0 || n_groups == 0) return 0;
@@ -203,7 +228,7 @@ extern "C" int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8,
     int* n_work = cv.take<int>(1);
     if (!cv.ok) return ERR_WORKSPACE;
     SkinnyArgs a{};
-    a.w = (const uint8_t*)w; a.w_estride = w_estride;
+    a.w = (const uint8_t*)w; a.w_estride = w_estride; a.n_experts = n_local_experts;
     a.s = (const uint8_t*)s; a.s_estride = s_estride;
     a.s_rstride = (K / 32) * (fmt == SK_FMT_FP4_BF16S ? 2 : 1);
     a.N = N; a.K = K;
@@ -214,7 +239,7 @@ extern "C" int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8,
     const int epi = accumulate ? SK_EPI_ATOMIC_F32 : SK_EPI_STORE_F32;
     int rc = skinny_check(a, fmt, epi);
     if (rc) return rc;
-    if (shard_n > (1 << 29)) shard_n = 1 << 29;
+    if (shard_n > n_local_experts) shard_n = n_local_experts;
     rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, work, n_work, n_pairs, stream);
     if (rc) return rc;
     if (zero_out && !accumulate) {
@@ -272,8 +297,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->has_shared && m->shared_fmt != SK_FMT_FP8_E8M0 && m->shared_fmt != SK_FMT_FP8_F32B) return ERR_UNSUPPORTED;
     if (m->score_mode < 0 || m->score_mode > 2) return ERR_UNSUPPORTED;
     if (m->workspace_bytes < b200_moe_workspace_bytes(T, topk, D, I) || ((uintptr_t)m->workspace & 255)) return ERR_WORKSPACE;
-    int shard_n = m->shard_n > (1 << 29) ? (1 << 29) : m->shard_n;
-    if (m->shard_start < 0 || shard_n < 0) return ERR_BAD_ARG;
+    const int shard_n = m->shard_n;  // = number of experts the shard tensors hold
+    if (m->shard_start < 0 || shard_n < 1 || shard_n > E) return ERR_BAD_ARG;
 
     Carver cv{(char*)m->workspace, m->workspace_bytes};
     __nv_bfloat16* xq = cv.take<__nv_bfloat16>((size_t)T * D);
@@ -310,7 +335,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
 
     // routed gate/up + SwiGLU * weight + fake quant -> hq [sorted pair, inter]
     SkinnyArgs a{};
-    a.w = (const uint8_t*)m->w13; a.w_estride = (long long)2 * I * (D / 2);
+    a.w = (const uint8_t*)m->w13; a.w_estride = (long long)2 * I * (D / 2); a.n_experts = shard_n;
     a.s = (const uint8_t*)m->s13; a.s_estride = (long long)2 * I * (D / 32) * sbytes; a.s_rstride = (D / 32) * sbytes;
     a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = D;
     a.work = work; a.n_work = n_work; a.pair_tok = pair_tok; a.pair_out = nullptr; a.pair_w = pair_w;
@@ -321,7 +346,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
     // routed down -> y2 [original pair, dim] fp32
     SkinnyArgs b{};
-    b.w = (const uint8_t*)m->w2; b.w_estride = (long long)D * (I / 2);
+    b.w = (const uint8_t*)m->w2; b.w_estride = (long long)D * (I / 2); b.n_experts = shard_n;
     b.s = (const uint8_t*)m->s2; b.s_estride = (long long)D * (I / 32) * sbytes; b.s_rstride = (I / 32) * sbytes;
     b.N = D; b.K = I; b.x = hq; b.x_ld = I;
     b.work = work; b.n_work = n_work; b.pair_tok = nullptr; b.pair_out = pair_out; b.pair_w = nullptr;

@@ -13,6 +13,7 @@
 // (dsv41/cuda/fp8_gemv_m1.cu:55) and fp8_gemm_tc8/16 (dsv41/cuda/fp8_tc.cu:53) with one kernel template.
 #include "common.cuh"
 #include "skinny.cuh"
+#include "tma.cuh"
 
 namespace b200 {
 
@@ -59,17 +60,25 @@ struct FmtTraits {
     static constexpr int CK = FP4 ? 128 : 64;  // k covered by one 16-byte load of each of the 4 lanes of a quad
 };
 
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(SK_CONSUMER_THREADS) : "memory"); }
+
+// Device-visible error word: a wait that ran out of time records where it gave up instead of spinning forever.
+__device__ int g_skinny_error = 0;
+
 // ------------------------------------------------------------------ activation tile
-// Fill the shared-memory activation tile for the tokens of one work.  16-byte unit u = ((c*A + i)*4 + t)*8 + g holds,
-// for token column g, the eight activations lane (g, t) needs for the two (FP4: word i of chunk c) or two (FP8: words
-// 2i, 2i+1) tensor-core steps, in (b0.lo, b0.hi, b1.lo, b1.hi) x 2 order.
+// Shared-memory activation tile of one work (<= 8 token columns), in the register order of the tensor-core tile: 16-byte
+// unit u = cu*32 + lane (lane = g*4 + t: token column g, quad lane t).  FP4: cu = k/32 (one 16-byte weight chunk of a row),
+// the unit holds x[k0 + {0,4,1,5,2,6,3,7}], k0 = 32 cu + 8 t, matching the code pairs (j, j+4) of the lane's weight word.
+// FP8: cu = k/32 covers the two 16-byte chunks 2 cu and 2 cu + 1; for each the unit holds x[kb + P(4t + {0,2,1,3})] with P
+// the byte order of the weight container.  A warp reads 32 consecutive units: no bank conflicts.  Values are pre-scaled by
+// 2^ACT_SHIFT.
 template <int FMT>
-__device__ void fill_act_tile(uint4* xs, const SkinnyArgs& a, int first, int ntok) {
+__device__ void fill_act_tile(uint4* xs, const SkinnyArgs& a, int first, int ntok, int tid) {
     constexpr bool FP4 = FmtTraits<FMT>::FP4;
     const int K = a.K;
     const float up = u32_as_f32((uint32_t)(127 + ACT_SHIFT) << 23);
-    for (int u = threadIdx.x; u < K; u += blockDim.x) {
-        const int g = u & 7, t = (u >> 3) & 3;
+    for (int u = tid; u < K; u += SK_CONSUMER_THREADS) {
+        const int t = u & 3, g = (u >> 2) & 7, cu = u >> 5;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (g < ntok) {
             const int pair = first + g;
@@ -77,8 +86,7 @@ __device__ void fill_act_tile(uint4* xs, const SkinnyArgs& a, int first, int nto
             const __nv_bfloat16* xr = a.x + row * a.x_ld;
             float f[8];
             if (FP4) {
-                const int i = (u >> 5) & 3, c = u >> 7;
-                const int k0 = c * 128 + t * 32 + i * 8;
+                const int k0 = cu * 32 + t * 8;
                 uint4 raw = *reinterpret_cast<const uint4*>(xr + k0);
                 uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
                 float e[8];
@@ -91,18 +99,14 @@ __device__ void fill_act_tile(uint4* xs, const SkinnyArgs& a, int first, int nto
 #pragma unroll
                     for (int j = 0; j < 8; ++j) e[j] = n[j];
                 }
-                // slot order 0,4,1,5,2,6,3,7: registers (x0,x4) (x1,x5) | (x2,x6) (x3,x7)
                 f[0] = e[0]; f[1] = e[4]; f[2] = e[1]; f[3] = e[5]; f[4] = e[2]; f[5] = e[6]; f[6] = e[3]; f[7] = e[7];
             } else {
-                const int h = (u >> 5) & 1, c = u >> 6;
-                const int kb = c * 64 + t * 16;
 #pragma unroll
                 for (int sl = 0; sl < 8; ++sl) {
-                    const int i = 2 * h + (sl >> 2);
-                    const int q = ((sl & 1) << 1) | ((sl >> 1) & 1);  // slot order 0,2,1,3 within a word
-                    const int p = 4 * i + q;
-                    const int k = kb + (a.w_permk ? PERM_K16[p] : p);
-                    f[sl] = __bfloat162float(xr[k]);
+                    const int kb = (2 * cu + (sl >> 2)) * 16;
+                    const int q = ((sl & 1) << 1) | ((sl >> 1) & 1);  // slot order 0,2,1,3 within the lane's word
+                    const int p = 4 * t + q;
+                    f[sl] = __bfloat162float(xr[kb + (a.w_permk ? PERM_K16[p] : p)]);
                 }
             }
             uint32_t o[4];
@@ -115,201 +119,293 @@ __device__ void fill_act_tile(uint4* xs, const SkinnyArgs& a, int first, int nto
 }
 
 // ------------------------------------------------------------------ the kernel
-constexpr int U = SK_CHUNKS_PER_BATCH;
-
-struct Batch {
-    uint4 wq[2][U];     // 16 weight bytes of rows g and g+8 for each chunk
-    uint32_t sc[2][U];  // raw scale bits for those loads
+// Work decomposition.  item = 64 weight rows of one work (SWIGLU epilogue: 32 gate rows + the 32 matching up rows).
+// The rows of an item are streamed in stages of 64 rows x 512 bytes: a producer thread issues eight TMA box loads
+// (32 rows x 128 bytes, 128-byte swizzle) per stage into a shared-memory ring and the bytes are counted on an mbarrier.
+// 16 consumer warps = 2 row halves x 8 slices of 64 bytes; per 16-byte chunk column a warp fetches its 32 rows with one
+// ldmatrix.x4 (conflict-free on the swizzled tile), dequantises the 32-bit words in registers and issues four
+// tensor-core tiles against the activation columns.
+struct ItemDesc {
+    int wk, it;        // work index, item index within the work
+    int expert, first, ntok;
+    int row0a, row0b;  // first weight row of each 32-row half
 };
 
 template <int FMT, int EPI>
-__global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs a) {
+__global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs a, const __grid_constant__ CUtensorMap tmap) {
     using T = FmtTraits<FMT>;
     constexpr bool FP4 = T::FP4;
-    constexpr int CK = T::CK;
-    extern __shared__ uint4 smem[];
-    uint4* xs = smem;                                       // K units of 16 B
-    float* red = reinterpret_cast<float*>(smem + a.K);      // [2][4 kq][4 rb][16][8]
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    const int K = a.K, N = a.N;
+    const int n_stages = a.n_stages;
+    // the swizzled boxes need 1024-byte alignment: round the dynamic window up (the launch reserves the slack)
+    uint8_t* ring = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);         // n_stages x 32 KB
+    uint4* xs = reinterpret_cast<uint4*>(ring + (size_t)n_stages * SK_STAGE_BYTES);      // K units of 16 B
+    float* red = reinterpret_cast<float*>(xs + K);                                       // [8 kq][64 rows][8 cols]
+    __shared__ __align__(8) unsigned long long bars[2 * SK_MAX_STAGES];                  // full[s], empty[s]
+    __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int rb = warp & 3, kq = warp >> 2;
-    const int K = a.K, N = a.N;
-    const int nchunks = K / CK;
-    const int nbat = (nchunks + U - 1) / U;
-    const int b0 = kq * nbat / 4, b1 = (kq + 1) * nbat / 4;
+    const long wrow_bytes = FP4 ? (K >> 1) : K;
+    const int nst = (int)((wrow_bytes + SK_STAGE_ROW_BYTES - 1) / SK_STAGE_ROW_BYTES);  // stages per item
+    const int n_units = K >> 5;                                                         // activation units per token column
     const int ipw = (EPI == SK_EPI_SWIGLU) ? (a.inter >> 5) : ((N + SK_ROWS - 1) / SK_ROWS);
     const int n_work = a.n_work ? *a.n_work : a.n_work_host;
     const long total = (long)n_work * ipw;
     const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-    const long wrow_bytes = FP4 ? (K >> 1) : K;
 
-    // dense mode (no work list): work wk = rows [8 wk, 8 wk + 8) of x against expert 0
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < n_stages; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[SK_MAX_STAGES + s]), SK_CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (lo >= hi) return;
+
     auto get_work = [&](int wk) -> int4 {
         if (a.work) return __ldg(a.work + wk);
-        const int rem = a.dense_rows - wk * SK_TOK;
+        const int rem = a.dense_rows - wk * SK_TOK;  // dense mode: work wk = rows [8 wk, 8 wk + 8) of x against expert 0
         return make_int4(0, wk * SK_TOK, rem < SK_TOK ? rem : SK_TOK, 0);
     };
-    auto row_base = [&](int it) -> int {
-        if (EPI == SK_EPI_SWIGLU) return (rb < 2) ? it * 32 + rb * 16 : a.inter + it * 32 + (rb - 2) * 16;
-        return it * SK_ROWS + rb * 16;
+    auto make_desc = [&](int wk, int it) -> ItemDesc {
+        ItemDesc d;
+        d.wk = wk; d.it = it;
+        const int4 w = get_work(wk);
+        d.expert = w.x; d.first = w.y; d.ntok = w.z;
+        if (EPI == SK_EPI_SWIGLU) { d.row0a = it * 32; d.row0b = a.inter + it * 32; }
+        else { d.row0a = it * SK_ROWS; d.row0b = it * SK_ROWS + 32; }
+        return d;
     };
+    auto next_desc = [&](const ItemDesc& d) -> ItemDesc {
+        int it = d.it + 1, wk = d.wk;
+        if (it == ipw) { it = 0; ++wk; }
+        return make_desc(wk, it);
+    };
+    const int wk_lo = (int)(lo / ipw), it_lo = (int)(lo - (long)wk_lo * ipw);
 
-    auto issue = [&](long item, int b, Batch& L) {
-        const int wk = (int)(item / ipw), it = (int)(item % ipw);
-        const int4 wrk = get_work(wk);
-        const int r0 = row_base(it);
-        const bool rows_ok = r0 < N;
-        const uint8_t* w0 = a.w + (long long)wrk.x * a.w_estride + (long)(r0 + g) * wrow_bytes + t * 16;
-        const uint8_t* w1 = w0 + 8 * wrow_bytes;
-        const uint8_t* sbase = a.s + (long long)wrk.x * a.s_estride;
+    if (warp == SK_CONSUMER_WARPS) {
+        // ------------------------------------------------ producer: one thread, eight box loads per stage
+        if (lane != 0) return;
+        tma_prefetch_desc(&tmap);
+        ItemDesc d = make_desc(wk_lo, it_lo);
+        uint32_t n = 0;
+        for (long item = lo; item < hi; ++item) {
+            for (int st = 0; st < nst; ++st, ++n) {
+                const uint32_t s = n % n_stages, ph = (n / n_stages) & 1;
+                const uint32_t full = smem_u32(&bars[s]), empty = smem_u32(&bars[SK_MAX_STAGES + s]);
+                if (!mbar_wait(empty, ph ^ 1, &abort_flag, &g_skinny_error, 1)) break;
+                mbar_expect_tx(full, SK_STAGE_BYTES);
+                const uint32_t dst = smem_u32(ring + (size_t)s * SK_STAGE_BYTES);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int c = b * U + u;
-            if (rows_ok && c < nchunks) {
-                L.wq[0][u] = ldg_stream16(w0 + c * 64);
-                L.wq[1][u] = ldg_stream16(w1 + c * 64);
-                if (FMT == SK_FMT_FP4_E8M0) {  // one byte per (row, 32 k): the chunk's four bytes, lane t uses byte t
-                    L.sc[0][u] = ldg_stream4(sbase + (long)(r0 + g) * a.s_rstride + 4 * c);
-                    L.sc[1][u] = ldg_stream4(sbase + (long)(r0 + g + 8) * a.s_rstride + 4 * c);
-                } else if (FMT == SK_FMT_FP4_BF16S) {  // one bf16 per (row, 32 k)
-                    L.sc[0][u] = *reinterpret_cast<const unsigned short*>(sbase + (long)(r0 + g) * a.s_rstride + 2 * (4 * c + t));
-                    L.sc[1][u] = *reinterpret_cast<const unsigned short*>(sbase + (long)(r0 + g + 8) * a.s_rstride + 2 * (4 * c + t));
-                } else if (FMT == SK_FMT_FP8_E8M0) {  // one byte per (32 rows, 32 k); rows g and g+8 share it
-                    L.sc[0][u] = *(sbase + (long)(r0 >> 5) * a.s_rstride + 2 * c + (t >> 1));
-                } else {  // one fp32 per (128 rows, 128 k)
-                    L.sc[0][u] = ldg_stream4(sbase + (long)(r0 >> 7) * a.s_rstride + 4 * (c >> 1));
+                for (int sl = 0; sl < 4; ++sl) {  // stage layout [row half][128-byte slab][32 rows][128 B]
+                    const int x = st * SK_STAGE_ROW_BYTES + sl * 128;
+                    tma_load_3d(dst + sl * 4096, &tmap, x, d.row0a, d.expert, full);
+                    tma_load_3d(dst + 16384 + sl * 4096, &tmap, x, d.row0b, d.expert, full);
                 }
-            } else {
-                L.wq[0][u] = make_uint4(0, 0, 0, 0);
-                L.wq[1][u] = make_uint4(0, 0, 0, 0);
-                L.sc[0][u] = 0;
-                L.sc[1][u] = 0;
             }
+            if (abort_flag) break;
+            if (item + 1 < hi) d = next_desc(d);
+        }
+        // leave only when every load this thread issued has landed (bounded wait on the last use of each ring slot)
+        for (int k = 0; k < n_stages && k < (int)n; ++k) {
+            const uint32_t m = n - 1 - k;
+            const uint32_t s = m % n_stages, ph = (m / n_stages) & 1;
+            const unsigned long long t0 = global_timer_ns();
+            while (!mbar_test(smem_u32(&bars[s]), ph)) {
+                if (global_timer_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(&g_skinny_error, 0, 3); break; }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------- consumer warps
+    const int rh = warp & 1, kq = warp >> 1;  // row half (32 rows), 64-byte slice of every stage row
+    ItemDesc d = make_desc(wk_lo, it_lo);
+    ItemDesc dn = d;
+    auto scale_ptr = [&](const ItemDesc& q, int j) -> const uint8_t* {  // scale row of weight row g + 8 j of this warp's half
+        const uint8_t* sb = a.s + (long long)q.expert * a.s_estride;
+        const int r = min((rh ? q.row0b : q.row0a) + g + 8 * j, N - 1);
+        if (FP4) return sb + (long)r * a.s_rstride;
+        if (FMT == SK_FMT_FP8_E8M0) return sb + (long)(r >> 5) * a.s_rstride;
+        return sb + (long)(r >> 7) * a.s_rstride;
+    };
+    // scale bits of this warp's slice of stage st.  FP4: k = 1024 st + 128 kq + [0, 128) = scale groups 4 c .. 4 c + 3 of the
+    // row, c = 8 st + kq (one byte or bf16 each).  FP8: k = 512 st + 64 kq + [0, 64) = groups 2 c, 2 c + 1 (E8M0 per 32 k) or the
+    // fp32 of block c >> 1 (per 128 k).
+    auto load_scales = [&](const ItemDesc& q, int st, uint32_t (&sc)[4], uint32_t (&sc2)[4]) {
+        const int c = st * 8 + kq;
+        if (c * (FP4 ? 128 : 64) >= K) { sc[0] = sc[1] = sc[2] = sc[3] = 0; sc2[0] = sc2[1] = sc2[2] = sc2[3] = 0; return; }
+        if (FMT == SK_FMT_FP4_E8M0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sc[j] = ldg_stream4(scale_ptr(q, j) + 4 * c);
+        } else if (FMT == SK_FMT_FP4_BF16S) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint2 v = *reinterpret_cast<const uint2*>(scale_ptr(q, j) + 8 * c);
+                sc[j] = v.x;
+                sc2[j] = v.y;
+            }
+        } else if (FMT == SK_FMT_FP8_E8M0) {
+            const uint8_t* sp = scale_ptr(q, 0) + 2 * c;
+            sc[0] = (uint32_t)sp[0] | ((uint32_t)sp[1] << 8);
+        } else {
+            sc[0] = ldg_stream4(scale_ptr(q, 0) + 4 * (c >> 1));
         }
     };
 
-    float acc[4];
-    auto compute = [&](int b, const Batch& L) {
-        float blk[4] = {0.f, 0.f, 0.f, 0.f};  // FP8 / fp32 block scales: partial sum of one 128-k block
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int c = b * U + u;
-            if (c >= nchunks) break;
-            if (FP4) {
-                uint32_t m0, m1;
-                if (FMT == SK_FMT_FP4_E8M0) {
-                    const uint32_t s0 = (L.sc[0][u] >> (8 * t)) & 0xFFu, s1 = (L.sc[1][u] >> (8 * t)) & 0xFFu;
-                    m0 = s0 ? bf16x2_pow2((int)s0 + 126 - ACT_SHIFT) : 0u;  // 2^(s - 127) * 2^126 * 2^-ACT_SHIFT
-                    m1 = s1 ? bf16x2_pow2((int)s1 + 126 - ACT_SHIFT) : 0u;
-                } else {
-                    const float up = u32_as_f32((uint32_t)(127 + 126 - ACT_SHIFT) << 23);
-                    uint32_t h0 = f32_to_bf16_bits(bf16_bits_to_f32(L.sc[0][u]) * up), h1 = f32_to_bf16_bits(bf16_bits_to_f32(L.sc[1][u]) * up);
-                    m0 = h0 | (h0 << 16);
-                    m1 = h1 | (h1 << 16);
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t p[4], q[4];
-                    dequant_fp4_word(word_of(L.wq[0][u], i), m0, p);
-                    dequant_fp4_word(word_of(L.wq[1][u], i), m1, q);
-                    const uint4 bv = lds128(xs + (((c * 4 + i) * 4 + t) * 8 + g));
-                    mma_bf16_16816(acc, p[0], q[0], p[1], q[1], bv.x, bv.y);
-                    mma_bf16_16816(acc, p[2], q[2], p[3], q[3], bv.z, bv.w);
-                }
-            } else {
-                uint32_t m;
-                if (FMT == SK_FMT_FP8_E8M0) {
-                    const uint32_t s0 = L.sc[0][u] & 0xFFu;
-                    m = s0 ? bf16x2_pow2((int)s0 + 120 - ACT_SHIFT) : 0u;  // 2^(s - 127) * 2^120 * 2^-ACT_SHIFT
-                } else {
-                    m = bf16x2_pow2(127 + 120 - ACT_SHIFT);
-                }
-                float* dst = (FMT == SK_FMT_FP8_F32B) ? blk : acc;
-                float (&d)[4] = *reinterpret_cast<float (*)[4]>(dst);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 bv = lds128(xs + (((c * 2 + h) * 4 + t) * 8 + g));
-                    uint32_t p[2], q[2];
-                    dequant_fp8_word(word_of(L.wq[0][u], 2 * h), m, p);
-                    dequant_fp8_word(word_of(L.wq[1][u], 2 * h), m, q);
-                    mma_bf16_16816(d, p[0], q[0], p[1], q[1], bv.x, bv.y);
-                    dequant_fp8_word(word_of(L.wq[0][u], 2 * h + 1), m, p);
-                    dequant_fp8_word(word_of(L.wq[1][u], 2 * h + 1), m, q);
-                    mma_bf16_16816(d, p[0], q[0], p[1], q[1], bv.z, bv.w);
-                }
-                if (FMT == SK_FMT_FP8_F32B && ((c & 1) || c + 1 == nchunks)) {
-                    const float sc = u32_as_f32(L.sc[0][u]);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) { acc[j] = fmaf(sc, blk[j], acc[j]); blk[j] = 0.f; }
-                }
-            }
-        }
-    };
-
-    Batch cur, nxt;
-    const bool has_k = b0 < b1;
-    if (lo < hi && has_k) issue(lo, b0, cur);
-    int cur_wk = -1, buf = 0;
-    int4 wrk = make_int4(0, 0, 0, 0);
+    uint32_t sc_cur[4], sc_nxt[4], sc2_cur[4] = {0, 0, 0, 0}, sc2_nxt[4] = {0, 0, 0, 0};
+    load_scales(d, 0, sc_cur, sc2_cur);
+    uint32_t n = 0;
+    int cur_wk = -1;
+    bool first_item = true;
+    // ldmatrix row address of this lane inside a 32-row box: row l at l*128, 16-byte chunk cc stored at chunk cc ^ (l & 7)
+    const uint32_t lm_row = (uint32_t)(rh * 16384 + (kq >> 1) * 4096 + lane * 128);
+    const uint32_t lm_x = (uint32_t)(lane & 7);
     for (long item = lo; item < hi; ++item) {
-        const int wk = (int)(item / ipw), it = (int)(item % ipw);
-        if (wk != cur_wk) {  // new work: the token columns change
-            __syncthreads();
-            wrk = get_work(wk);
-            fill_act_tile<FMT>(xs, a, wrk.y, wrk.z);
-            __syncthreads();
-            cur_wk = wk;
+        if (d.wk != cur_wk) {  // new work: the token columns change (every warp is past the previous item's compute)
+            if (!first_item) consumer_sync();
+            fill_act_tile<FMT>(xs, a, d.first, d.ntok, tid);
+            consumer_sync();
+            cur_wk = d.wk;
         }
+        const bool has_next = item + 1 < hi;
+        if (has_next) dn = next_desc(d);
+        float acc[2][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] = 0.f;
-        for (int b = b0; b < b1; ++b) {
-            const bool more = b + 1 < b1;
-            if (more) issue(item, b + 1, nxt);
-            else if (item + 1 < hi) issue(item + 1, b0, nxt);
-            compute(b, cur);
-            cur = nxt;
-        }
-        // partial sums of the 4 K splits -> shared memory
-        float* rp = red + ((((buf * 4 + kq) * 4 + rb) * 16) * 8);
-        *reinterpret_cast<float2*>(rp + g * 8 + 2 * t) = make_float2(acc[0], acc[1]);
-        *reinterpret_cast<float2*>(rp + (g + 8) * 8 + 2 * t) = make_float2(acc[2], acc[3]);
-        __syncthreads();
-        const float* rbuf = red + buf * (4 * 4 * 16 * 8);
-        const int ntok = wrk.z, first = wrk.y;
-        if (EPI == SK_EPI_SWIGLU) {
-            // warp = token column, lane = column of the 32-wide quantisation group (dsv41/fused.py:285-306)
-            if (warp < ntok) {
-                const int rg = lane >> 4, row = lane & 15;
-                float gt = 0.f, up = 0.f;
+        for (int j = 0; j < 4; ++j) acc[0][j] = acc[1][j] = 0.f;
+        const bool bcol = g < d.ntok;
+        for (int st = 0; st < nst; ++st, ++n) {
+            const uint32_t s = n % n_stages, ph = (n / n_stages) & 1;
+            // scales of the next stage (possibly of the next item) travel while this stage is computed
+            if (st + 1 < nst) load_scales(d, st + 1, sc_nxt, sc2_nxt);
+            else if (has_next) load_scales(dn, 0, sc_nxt, sc2_nxt);
+            const bool ready = mbar_wait(smem_u32(&bars[s]), ph, &abort_flag, &g_skinny_error, 2);
+            const int c = st * 8 + kq;
+            if (ready) {
+                const uint32_t box = smem_u32(ring + (size_t)s * SK_STAGE_BYTES) + lm_row;
+                if (FP4) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    gt += rbuf[(((q * 4 + rg) * 16) + row) * 8 + warp];
-                    up += rbuf[(((q * 4 + 2 + rg) * 16) + row) * 8 + warp];
+                    for (int i = 0; i < 4; ++i) {  // chunk column i of the slice = scale group 4 c + i
+                        const int cu = 4 * c + i;
+                        uint32_t w[4];
+                        ldmatrix_x4(box + ((((kq & 1) * 4 + i) ^ lm_x) << 4), w);
+                        uint4 bv = make_uint4(0, 0, 0, 0);
+                        if (bcol && cu < n_units) bv = lds128(xs + (cu * 32 + lane));
+                        uint32_t mult[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (FMT == SK_FMT_FP4_E8M0) {
+                                // both halves = 2^(s - 127) * 2^126 * 2^-ACT_SHIFT: exponent field s + 94.  Scale byte 0 needs no
+                                // special case: the product with a code (<= 6 * 2^-126) underflows to zero in bf16.
+                                mult[j] = __byte_perm(sc_cur[j], 0, 0x4440 | i) * 0x00800080u + bf16x2_pow2(126 - ACT_SHIFT);
+                            } else {
+                                const uint32_t raw = ((i & 2) ? sc2_cur[j] : sc_cur[j]) >> ((i & 1) * 16) & 0xFFFFu;
+                                const float up = u32_as_f32((uint32_t)(127 + 126 - ACT_SHIFT) << 23);
+                                const uint32_t h0 = f32_to_bf16_bits(bf16_bits_to_f32(raw) * up);
+                                mult[j] = h0 | (h0 << 16);
+                            }
+                        }
+                        uint32_t p0[4], p1[4], p2[4], p3[4];
+                        dequant_fp4_word(w[0], mult[0], p0);
+                        dequant_fp4_word(w[1], mult[1], p1);
+                        dequant_fp4_word(w[2], mult[2], p2);
+                        dequant_fp4_word(w[3], mult[3], p3);
+                        mma_bf16_16816(acc[0], p0[0], p1[0], p0[1], p1[1], bv.x, bv.y);
+                        mma_bf16_16816(acc[0], p0[2], p1[2], p0[3], p1[3], bv.z, bv.w);
+                        mma_bf16_16816(acc[1], p2[0], p3[0], p2[1], p3[1], bv.x, bv.y);
+                        mma_bf16_16816(acc[1], p2[2], p3[2], p2[3], p3[3], bv.z, bv.w);
+                    }
+                } else {
+                    float blk[2][4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) blk[0][j] = blk[1][j] = 0.f;
+                    float (&d0)[4] = (FMT == SK_FMT_FP8_F32B) ? blk[0] : acc[0];
+                    float (&d1)[4] = (FMT == SK_FMT_FP8_F32B) ? blk[1] : acc[1];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {  // 32-k scale group h of the slice = activation unit 2 c + h
+                        const int cu = 2 * c + h;
+                        uint32_t m;
+                        if (FMT == SK_FMT_FP8_E8M0) {
+                            // 2^(s - 127) * 2^120 * 2^-ACT_SHIFT: exponent field s + 88 (byte 0 underflows to zero like above)
+                            m = __byte_perm(sc_cur[0], 0, 0x4440 | h) * 0x00800080u + bf16x2_pow2(120 - ACT_SHIFT);
+                        } else {
+                            m = bf16x2_pow2(127 + 120 - ACT_SHIFT);
+                        }
+                        uint4 bv = make_uint4(0, 0, 0, 0);
+                        if (bcol && cu < n_units) bv = lds128(xs + (cu * 32 + lane));
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {  // 16-byte chunk column 2 h + e of the slice
+                            uint32_t w[4];
+                            ldmatrix_x4(box + ((((kq & 1) * 4 + 2 * h + e) ^ lm_x) << 4), w);
+                            uint32_t p0[2], p1[2], p2[2], p3[2];
+                            dequant_fp8_word(w[0], m, p0);
+                            dequant_fp8_word(w[1], m, p1);
+                            dequant_fp8_word(w[2], m, p2);
+                            dequant_fp8_word(w[3], m, p3);
+                            const uint32_t b0 = e ? bv.z : bv.x, b1 = e ? bv.w : bv.y;
+                            mma_bf16_16816(d0, p0[0], p1[0], p0[1], p1[1], b0, b1);
+                            mma_bf16_16816(d1, p2[0], p3[0], p2[1], p3[1], b0, b1);
+                        }
+                    }
+                    if (FMT == SK_FMT_FP8_F32B) {
+                        const float scl = u32_as_f32(sc_cur[0]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { acc[0][j] = fmaf(scl, blk[0][j], acc[0][j]); acc[1][j] = fmaf(scl, blk[1][j], acc[1][j]); }
+                    }
                 }
-                if (a.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars[SK_MAX_STAGES + s]));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { sc_cur[j] = sc_nxt[j]; sc2_cur[j] = sc2_nxt[j]; }
+        }
+        // partial sums of the 8 slices -> shared memory (after every warp has finished reading the previous item's sums)
+        if (!first_item) consumer_sync();
+        first_item = false;
+        float* rp = red + (kq * 64 + rh * 32) * 8;
+        *reinterpret_cast<float2*>(rp + g * 8 + 2 * t) = make_float2(acc[0][0], acc[0][1]);
+        *reinterpret_cast<float2*>(rp + (g + 8) * 8 + 2 * t) = make_float2(acc[0][2], acc[0][3]);
+        *reinterpret_cast<float2*>(rp + (g + 16) * 8 + 2 * t) = make_float2(acc[1][0], acc[1][1]);
+        *reinterpret_cast<float2*>(rp + (g + 24) * 8 + 2 * t) = make_float2(acc[1][2], acc[1][3]);
+        consumer_sync();
+        const int ntok = d.ntok, first = d.first, it = d.it;
+        if (EPI == SK_EPI_SWIGLU) {
+            // warp = token column, lane = column of the 32-wide quantisation group (dsv41/fused.py:285-306):
+            // half 0 of the item holds the gate rows, half 1 the up rows
+            if (warp < ntok) {
+                float gt = 0.f, upv = 0.f;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    gt += red[(q * 64 + lane) * 8 + warp];
+                    upv += red[(q * 64 + 32 + lane) * 8 + warp];
+                }
+                if (a.round_gu_bf16) { gt = round_bf16(gt); upv = round_bf16(upv); }
                 const int pair = first + warp;
-                const float h = swiglu_bf16(gt, up, a.pair_w ? a.pair_w[pair] : 1.f, a.limit);
+                const float h = swiglu_bf16(gt, upv, a.pair_w ? a.pair_w[pair] : 1.f, a.limit);
                 const float s = fp8_group_scale(warp_max(fabsf(h)));
                 const long orow = a.pair_out ? a.pair_out[pair] : pair;
                 reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + it * 32 + lane] = __float2bfloat16_rn(fp8_fake_quant_value(h, s));
             }
         } else {
             const int col = tid >> 6, rr = tid & 63;
-            const int n = it * SK_ROWS + rr;
-            if (col < ntok && n < N) {
+            const int nrow = it * SK_ROWS + rr;
+            if (col < ntok && nrow < N) {
                 float v = 0.f;
 #pragma unroll
-                for (int q = 0; q < 4; ++q) v += rbuf[(((q * 4 + (rr >> 4)) * 16) + (rr & 15)) * 8 + col];
+                for (int q = 0; q < 8; ++q) v += red[(q * 64 + rr) * 8 + col];
                 const int pair = first + col;
                 if (a.pair_w) v *= a.pair_w[pair];
                 const long orow = a.pair_out ? a.pair_out[pair] : pair;
-                if (EPI == SK_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + n] = v;
-                else if (EPI == SK_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow * a.out_ld + n, v);
-                else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + n] = __float2bfloat16_rn(v);
+                if (EPI == SK_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + nrow] = v;
+                else if (EPI == SK_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow, v);
+                else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + nrow] = __float2bfloat16_rn(v);
             }
         }
-        buf ^= 1;
+        if (has_next) d = dn;
     }
 }
 
@@ -387,27 +483,27 @@ int sm_count() {
 }
 
 template <int FMT, int EPI>
-static int launch_one(const SkinnyArgs& a, int grid, size_t smem, cudaStream_t stream) {
+static int launch_one(const SkinnyArgs& a, const CUtensorMap& tm, int grid, size_t smem, cudaStream_t stream) {
     static bool attr_done[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(skinny_kernel<FMT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(skinny_kernel<FMT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_LIMIT);
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    skinny_kernel<FMT, EPI><<<grid, SK_THREADS, smem, stream>>>(a);
+    skinny_kernel<FMT, EPI><<<grid, SK_THREADS, smem, stream>>>(a, tm);
     B200_CHECK_LAUNCH();
     return 0;
 }
 
 template <int FMT>
-static int launch_fmt(const SkinnyArgs& a, int epi, int grid, size_t smem, cudaStream_t stream) {
+static int launch_fmt(const SkinnyArgs& a, const CUtensorMap& tm, int epi, int grid, size_t smem, cudaStream_t stream) {
     switch (epi) {
-        case SK_EPI_STORE_F32: return launch_one<FMT, SK_EPI_STORE_F32>(a, grid, smem, stream);
-        case SK_EPI_ATOMIC_F32: return launch_one<FMT, SK_EPI_ATOMIC_F32>(a, grid, smem, stream);
-        case SK_EPI_SWIGLU: return launch_one<FMT, SK_EPI_SWIGLU>(a, grid, smem, stream);
-        case SK_EPI_STORE_BF16: return launch_one<FMT, SK_EPI_STORE_BF16>(a, grid, smem, stream);
+        case SK_EPI_STORE_F32: return launch_one<FMT, SK_EPI_STORE_F32>(a, tm, grid, smem, stream);
+        case SK_EPI_ATOMIC_F32: return launch_one<FMT, SK_EPI_ATOMIC_F32>(a, tm, grid, smem, stream);
+        case SK_EPI_SWIGLU: return launch_one<FMT, SK_EPI_SWIGLU>(a, tm, grid, smem, stream);
+        case SK_EPI_STORE_BF16: return launch_one<FMT, SK_EPI_STORE_BF16>(a, tm, grid, smem, stream);
     }
     return ERR_UNSUPPORTED;
 }
@@ -417,25 +513,35 @@ int skinny_check(const SkinnyArgs& a, int fmt, int epi) {
     if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
     const bool fp4 = fmt == SK_FMT_FP4_E8M0 || fmt == SK_FMT_FP4_BF16S;
     if (a.K <= 0 || a.N <= 0 || a.K % (fp4 ? 128 : 64) || a.N % 16) return ERR_BAD_SHAPE;
-    if ((size_t)a.K * 16 + SK_RED_BYTES > 200 * 1024) return ERR_BAD_SHAPE;
+    if ((size_t)a.K * 16 + SK_RED_BYTES + 1024 + 2 * SK_STAGE_BYTES > (size_t)SK_SMEM_LIMIT) return ERR_BAD_SHAPE;  // K <= 9088
     if (epi == SK_EPI_SWIGLU && (a.inter <= 0 || a.inter % 32 || a.N != 2 * a.inter)) return ERR_BAD_SHAPE;
     if (((uintptr_t)a.w & 15) || (a.w_estride & 15) || ((uintptr_t)a.x & 15) || (a.x_ld & 7)) return ERR_BAD_ALIGN;
     if (fmt == SK_FMT_FP4_E8M0 && (((uintptr_t)a.s & 3) || (a.s_rstride & 3) || (a.s_estride & 3))) return ERR_BAD_ALIGN;
     if (fmt == SK_FMT_FP8_F32B && (((uintptr_t)a.s & 3) || (a.s_rstride & 3))) return ERR_BAD_ALIGN;
-    if (fmt == SK_FMT_FP4_BF16S && (((uintptr_t)a.s & 1) || (a.s_rstride & 1) || (a.s_estride & 1))) return ERR_BAD_ALIGN;
+    if (fmt == SK_FMT_FP4_BF16S && (((uintptr_t)a.s & 7) || (a.s_rstride & 7) || (a.s_estride & 7))) return ERR_BAD_ALIGN;
     return 0;
 }
 
-int skinny_launch(const SkinnyArgs& a, int fmt, int epi, cudaStream_t stream) {
-    int rc = skinny_check(a, fmt, epi);
+int skinny_launch(const SkinnyArgs& a_in, int fmt, int epi, cudaStream_t stream) {
+    int rc = skinny_check(a_in, fmt, epi);
     if (rc) return rc;
-    const size_t smem = (size_t)a.K * 16 + SK_RED_BYTES;
+    SkinnyArgs a = a_in;
+    const size_t fixed = (size_t)a.K * 16 + SK_RED_BYTES + 1024;
+    int stages = (int)(((size_t)SK_SMEM_LIMIT - fixed) / SK_STAGE_BYTES);
+    if (stages > SK_MAX_STAGES) stages = SK_MAX_STAGES;
+    a.n_stages = stages;
+    const size_t smem = fixed + (size_t)stages * SK_STAGE_BYTES;
     const int grid = sm_count();
+    const bool fp4 = fmt == SK_FMT_FP4_E8M0 || fmt == SK_FMT_FP4_BF16S;
+    const uint64_t row_bytes = fp4 ? (uint64_t)a.K / 2 : (uint64_t)a.K;
+    alignas(64) CUtensorMap tm;
+    rc = make_weight_tmap(&tm, a.w, row_bytes, (uint64_t)a.N, (uint64_t)(a.n_experts > 0 ? a.n_experts : 1), (uint64_t)a.w_estride, 32);
+    if (rc) return rc;
     switch (fmt) {
-        case SK_FMT_FP4_E8M0: return launch_fmt<SK_FMT_FP4_E8M0>(a, epi, grid, smem, stream);
-        case SK_FMT_FP4_BF16S: return launch_fmt<SK_FMT_FP4_BF16S>(a, epi, grid, smem, stream);
-        case SK_FMT_FP8_E8M0: return launch_fmt<SK_FMT_FP8_E8M0>(a, epi, grid, smem, stream);
-        case SK_FMT_FP8_F32B: return launch_fmt<SK_FMT_FP8_F32B>(a, epi, grid, smem, stream);
+        case SK_FMT_FP4_E8M0: return launch_fmt<SK_FMT_FP4_E8M0>(a, tm, epi, grid, smem, stream);
+        case SK_FMT_FP4_BF16S: return launch_fmt<SK_FMT_FP4_BF16S>(a, tm, epi, grid, smem, stream);
+        case SK_FMT_FP8_E8M0: return launch_fmt<SK_FMT_FP8_E8M0>(a, tm, epi, grid, smem, stream);
+        case SK_FMT_FP8_F32B: return launch_fmt<SK_FMT_FP8_F32B>(a, tm, epi, grid, smem, stream);
     }
     return ERR_UNSUPPORTED;
 }

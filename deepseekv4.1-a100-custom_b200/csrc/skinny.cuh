@@ -6,11 +6,16 @@
 
 namespace b200 {
 
-constexpr int SK_THREADS = 512;         // 16 warps: 4 row blocks x 4 splits of K
-constexpr int SK_ROWS = 64;             // weight rows per item
-constexpr int SK_TOK = 8;               // token columns per work (one 8-wide tensor-core tile)
-constexpr int SK_CHUNKS_PER_BATCH = 4;  // 16-byte loads per row in flight per lane
-constexpr int SK_RED_BYTES = 2 * 4 * 4 * 16 * 8 * 4;
+constexpr int SK_CONSUMER_WARPS = 16;    // 2 row halves x 8 slices of 64 bytes
+constexpr int SK_CONSUMER_THREADS = SK_CONSUMER_WARPS * 32;
+constexpr int SK_THREADS = SK_CONSUMER_THREADS + 32;  // + 1 producer warp (bulk copies)
+constexpr int SK_ROWS = 64;              // weight rows per item
+constexpr int SK_TOK = 8;                // token columns per work (one 8-wide tensor-core tile)
+constexpr int SK_STAGE_ROW_BYTES = 512;  // bytes of each row per stage
+constexpr int SK_STAGE_BYTES = SK_ROWS * SK_STAGE_ROW_BYTES;  // eight boxes of 32 rows x 128 bytes
+constexpr int SK_MAX_STAGES = 8;
+constexpr int SK_RED_BYTES = 8 * 64 * 8 * 4;  // partial sums of the 8 slices
+constexpr int SK_SMEM_LIMIT = 227 * 1024 - 2048;
 
 // weight formats (also the `fmt` values of the C-ABI)
 enum { SK_FMT_FP4_E8M0 = 0, SK_FMT_FP4_BF16S = 1, SK_FMT_FP8_E8M0 = 2, SK_FMT_FP8_F32B = 3 };
@@ -20,6 +25,7 @@ enum { SK_EPI_STORE_F32 = 0, SK_EPI_ATOMIC_F32 = 1, SK_EPI_SWIGLU = 2, SK_EPI_ST
 struct SkinnyArgs {
     const uint8_t* w;       // weights: [experts][N][K/2] packed E2M1 or [experts][N][K] e4m3
     long long w_estride;    // bytes between experts
+    int n_experts;          // experts held by w (bounds of the tensor map); 0 = 1
     const uint8_t* s;       // scales (format dependent)
     long long s_estride;    // bytes between experts
     int s_rstride;          // bytes between scale rows (FP4: per weight row; FP8: per 32- or 128-row block)
@@ -40,6 +46,7 @@ struct SkinnyArgs {
     float limit;            // SwiGLU clamp (epilogue SK_EPI_SWIGLU)
     int inter;              // N == 2*inter for SK_EPI_SWIGLU
     int round_gu_bf16;      // round gate/up to bf16 before SwiGLU (shared expert)
+    int n_stages;           // ring depth, set by skinny_launch from the shared-memory budget
 };
 
 int sm_count();

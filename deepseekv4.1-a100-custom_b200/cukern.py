@@ -48,7 +48,7 @@ def grouped_fp4(x, w, s, grp_expert, grp_start, grp_count, pair_tok, pair_out, p
     ws = L.workspace(dev, nbytes, "fp4_grouped")
     with torch.cuda.device(dev):
         rc = lib.b200_fp4_grouped_gemm(L.ptr(x), x.stride(0), int(bool(x_perm8)), L.ptr(w), w.stride(0) * w.element_size(), L.ptr(s),
-                                       s.stride(0) * s.element_size(), _fp4_fmt(s), N, K, L.ptr(ge), L.ptr(gs), L.ptr(gc), G, L.ptr(pt), L.ptr(po),
+                                       s.stride(0) * s.element_size(), _fp4_fmt(s), E, N, K, L.ptr(ge), L.ptr(gs), L.ptr(gc), G, L.ptr(pt), L.ptr(po),
                                        L.ptr(pw), int(n_pairs), int(shard_start), int(min(shard_n, 1 << 30)), int(bool(zero_out)),
                                        int(bool(accumulate)), L.ptr(out), out.stride(0), L.ptr(ws), ws.numel(), L.stream_of(dev))
     L.check(rc, "b200_fp4_grouped_gemm")

@@ -84,19 +84,19 @@ int b200_permute_x8(const void* x, void* y, long long n_elems, cudaStream_t stre
  * (dsv41/cukern.py:286-306) and fp4_gemm_tc (dsv41/cukern.py:309-344); with accumulate != 0 it has the scatter-add
  * contract of grouped_fp4_gemm (dsv41/moe_kernels.py:161-231).
  *   out[pair_out[p], :] (+)= pair_w[p] * x[pair_tok[p], :] @ W[grp_expert[g] - shard_start]^T   for p in group g
- *   x bf16 [rows, K] with row stride x_ld elements (x_perm8: the 8-k permuted layout); w uint8 [n, N, K/2],
+ *   x bf16 [rows, K] with row stride x_ld elements (x_perm8: the 8-k permuted layout); w uint8 [n_local_experts, N, K/2],
  *   s [n, N, K/32] (fmt B200_FMT_FP4_E8M0: bytes, B200_FMT_FP4_BF16S: bf16); w_estride / s_estride in BYTES;
  *   grp_expert int32 [n_groups] (global ids, -1 = padding); group g owns pairs grp_start[g] .. +count-1 with count =
  *   grp_count[g], or grp_start[g+1] - grp_start[g] when grp_count is NULL (then grp_start has n_groups+1 entries,
  *   dsv41/decode.py:431-432; the grp_count form is the tile table of dsv41/moe_kernels.py:118-132); pair_tok / pair_out int32
  *   [n_pairs] or NULL (= pair index); pair_w fp32 [n_pairs] or NULL; out fp32, row stride out_ld elements.
  *   Groups whose expert is outside [shard_start, shard_start + shard_n) are skipped; with zero_out their rows are
- *   zeroed (dsv41/cuda/fp4_tc.cu:66-72).  K % 128 == 0, N % 16 == 0, K <= 11264.  Groups of any size are accepted;
+ *   zeroed (dsv41/cuda/fp4_tc.cu:66-72).  K % 128 == 0, N % 16 == 0, K <= 9088.  Groups of any size are accepted;
  *   more than 8 pairs re-read the expert once per 8.
  *   workspace: b200_fp4_grouped_workspace_bytes(n_pairs) bytes, 16-byte aligned. */
 size_t b200_fp4_grouped_workspace_bytes(int n_pairs);
 int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s, long long s_estride, int fmt,
-                          int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count, int n_groups, const int* pair_tok, const int* pair_out,
+                          int n_local_experts, int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count, int n_groups, const int* pair_tok, const int* pair_out,
                           const float* pair_w, int n_pairs, int shard_start, int shard_n, int zero_out, int accumulate, float* out, long long out_ld,
                           void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
@@ -105,7 +105,7 @@ int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void
  *   out[m, :] = x[m, :] @ dequant(w8, s)^T;  x bf16 [M, K] (row stride x_ld); w8 e4m3 [N, K];
  *   fmt B200_FMT_FP8_E8M0: s uint8 [ceil(N/32), s_cols]; B200_FMT_FP8_F32B: s fp32 [ceil(N/128), s_cols];
  *   w_permk != 0: weight bytes in the 16-k order of dsv41/w8.py:21-23 (what W8 holds);
- *   out bf16 (out_is_f32 = 0) or fp32, row stride out_ld.  K % 64 == 0, N % 16 == 0, K <= 11264.  Any M; the weights
+ *   out bf16 (out_is_f32 = 0) or fp32, row stride out_ld.  K % 64 == 0, N % 16 == 0, K <= 9088.  Any M; the weights
  *   are read once per 8 rows. */
 int b200_fp8_gemm(const void* x, long long x_ld, int M, const void* w8, const void* s, int fmt, int s_cols, int w_permk, int N, int K, void* out,
                   int out_is_f32, long long out_ld, cudaStream_t stream);
