@@ -29,7 +29,7 @@ class MoeArgs(ctypes.Structure):
                 ("has_shared", c_i), ("sh_w13", c_p), ("sh_s13", c_p), ("sh_w2", c_p), ("sh_s2", c_p),
                 ("shared_fmt", c_i), ("sh_s13_cols", c_i), ("sh_s2_cols", c_i), ("sh_permk", c_i), ("swiglu_limit", c_f),
                 ("out", c_p), ("routed_out", c_p), ("eid_out", c_p), ("wt_out", c_p), ("workspace", c_p), ("workspace_bytes", c_sz),
-                ("prof_start", c_p), ("prof_stop", c_p)]
+                ("prof_start", c_p), ("prof_stop", c_p), ("engine", c_i)]
 
 
 _SIGNATURES = {
@@ -48,6 +48,11 @@ _SIGNATURES = {
     "b200_fp8_gemm": (c_i, [c_p, c_ll, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_ll, c_p]),
     "b200_moe_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "b200_moe_forward": (c_i, [ctypes.POINTER(MoeArgs), c_p]),
+    "b200_mx_quantize_rows": (c_i, [c_p, c_ll, c_p, c_i, c_i, c_p, c_p, c_p]),
+    "b200_mx_grouped_workspace_bytes": (c_sz, [c_i]),
+    "b200_mx_grouped_gemm": (c_i, [c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_i, c_i, c_p, c_ll, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_f,
+                                   c_i, c_p, c_ll, c_p, c_i, c_i, c_p, c_sz, c_p]),
+    "b200_device_error": (c_i, [c_p, c_p]),
 }
 
 _lib = None

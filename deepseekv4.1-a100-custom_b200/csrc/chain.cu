@@ -4,6 +4,7 @@
 // work list) followed by the weight-streaming skinny GEMMs (skinny.cu) with fused epilogues and a final combine.
 #include "common.cuh"
 #include "skinny.cuh"
+#include "mxgemm.cuh"
 #include "router.cuh"
 #include "b200_moe.h"
 
@@ -12,6 +13,7 @@ namespace b200 {
 constexpr int ROUTE_THREADS = 128;
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
+constexpr int MX_ND_DECODE = 16;        // token columns per work of the block-scaled tensor-core path
 
 struct RouteArgs {
     int tokens, E, topk, dim;
@@ -23,6 +25,7 @@ struct RouteArgs {
     const __nv_bfloat16* x;
     __nv_bfloat16* xq;  // nullptr: x is already quantised
     int shard_start, shard_n;
+    int tpw;            // pairs per work
     int* eid;           // [tokens, topk]
     float* wt;          // [tokens, topk]
     int* pair_tok;      // sorted position -> token
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
         const int e = tid * per + i;
         if (e < E) {
             loc_p += s_cnt[e];
-            if (e >= a.shard_start && e < a.shard_start + a.shard_n) loc_w += (s_cnt[e] + SK_TOK - 1) / SK_TOK;
+            if (e >= a.shard_start && e < a.shard_start + a.shard_n) loc_w += (s_cnt[e] + a.tpw - 1) / a.tpw;
         }
     }
     int inc_p = loc_p, inc_w = loc_w;
@@ -121,7 +124,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
             s_start[e] = run_p;
             s_woff[e] = run_w;
             run_p += s_cnt[e];
-            if (e >= a.shard_start && e < a.shard_start + a.shard_n) run_w += (s_cnt[e] + SK_TOK - 1) / SK_TOK;
+            if (e >= a.shard_start && e < a.shard_start + a.shard_n) run_w += (s_cnt[e] + a.tpw - 1) / a.tpw;
         }
     }
     __syncthreads();
@@ -143,10 +146,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
             pos += __popc(m);
         }
         if (e >= a.shard_start && e < a.shard_start + a.shard_n) {
-            const int nsub = (cnt + SK_TOK - 1) / SK_TOK;
+            const int nsub = (cnt + a.tpw - 1) / a.tpw;
             for (int i = lane; i < nsub; i += 32) {
-                const int rem = cnt - i * SK_TOK;
-                a.work[s_woff[e] + i] = make_int4(e - a.shard_start, s_start[e] + i * SK_TOK, rem < SK_TOK ? rem : SK_TOK, e);
+                const int rem = cnt - i * a.tpw;
+                a.work[s_woff[e] + i] = make_int4(e - a.shard_start, s_start[e] + i * a.tpw, rem < a.tpw ? rem : a.tpw, e);
             }
         }
     }
@@ -281,6 +284,11 @@ extern "C" size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int in
     b += rnd256((size_t)tokens * inter * 2);  // hs
     b += rnd256(P * dim * 4);               // y2
     b += rnd256((size_t)tokens * dim * 2);  // ys
+    // block-scaled tensor-core path: activations as e4m3 bytes + E8M0 scale bytes
+    b += rnd256((P + 128) * dim) + rnd256((P + 128) * (dim / 32));                          // x8s, xsfs (pair-sorted gather)
+    b += rnd256(((size_t)tokens + 128) * dim) + rnd256(((size_t)tokens + 128) * (dim / 32));    // x8t, xsft
+    b += rnd256((P + 128) * inter) + rnd256((P + 128) * (inter / 32));                      // hq8, hsf
+    b += rnd256(((size_t)tokens + 128) * inter) + rnd256(((size_t)tokens + 128) * (inter / 32));  // hs8, hssf
     return b + 256;
 }
 
@@ -314,7 +322,20 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     __nv_bfloat16* hs = cv.take<__nv_bfloat16>((size_t)T * I);
     float* y2 = cv.take<float>((size_t)P * D);
     __nv_bfloat16* ys = cv.take<__nv_bfloat16>((size_t)T * D);
+    uint8_t* x8s = cv.take<uint8_t>((size_t)(P + 128) * D);
+    uint8_t* xsfs = cv.take<uint8_t>((size_t)(P + 128) * (D / 32));
+    uint8_t* x8t = cv.take<uint8_t>((size_t)(T + 128) * D);
+    uint8_t* xsft = cv.take<uint8_t>((size_t)(T + 128) * (D / 32));
+    uint8_t* hq8 = cv.take<uint8_t>((size_t)(P + 128) * I);
+    uint8_t* hsf = cv.take<uint8_t>((size_t)(P + 128) * (I / 32));
+    uint8_t* hs8 = cv.take<uint8_t>((size_t)(T + 128) * I);
+    uint8_t* hssf = cv.take<uint8_t>((size_t)(T + 128) * (I / 32));
     if (!cv.ok) return ERR_WORKSPACE;
+    // engine: 1 = streaming bf16 path (any scale format), 2 = block-scaled tensor cores (E8M0 scales, natural k order of the
+    // shared expert); 0 = choose 2 when the formats allow it
+    const bool mx_ok = m->expert_fmt == SK_FMT_FP4_E8M0 && (!m->has_shared || (m->shared_fmt == SK_FMT_FP8_E8M0 && !m->sh_permk)) && D % 128 == 0 && I % 128 == 0;
+    if (m->engine == 2 && !mx_ok) return ERR_UNSUPPORTED;
+    const bool use_mx = m->engine == 2 || (m->engine == 0 && mx_ok);
 
     // the counter of the "last block" election must start at zero; it resets itself after every launch
     cudaError_t ce = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
@@ -325,11 +346,59 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     r.logits_f32 = m->logits_is_bf16 ? nullptr : (const float*)m->logits;
     r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
     r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
-    r.x = (const __nv_bfloat16*)m->x; r.xq = m->x_is_quantized ? nullptr : xq;
-    r.shard_start = m->shard_start; r.shard_n = shard_n;
+    r.x = (const __nv_bfloat16*)m->x; r.xq = (m->x_is_quantized || use_mx) ? nullptr : xq;
+    r.shard_start = m->shard_start; r.shard_n = shard_n; r.tpw = use_mx ? MX_ND_DECODE : SK_TOK;
     r.eid = eid; r.wt = wt; r.pair_tok = pair_tok; r.pair_out = pair_out; r.pair_w = pair_w; r.work = work; r.n_work = n_work; r.counter = counter;
     moe_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
     B200_CHECK_LAUNCH();
+    if (use_mx) {
+        const bool shared = m->has_shared && m->out;
+        // activations -> e4m3 + E8M0 (the FP8 fake quantisation kept in quantised form), gathered into pair-sorted order
+        int rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, pair_tok, (int)P, D, x8s, xsfs, stream);
+        if (rc) return rc;
+        if (shared && (rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, nullptr, T, D, x8t, xsft, stream))) return rc;
+        MxArgs g1{};
+        g1.w = m->w13; g1.w_estride = (long long)2 * I * (D / 2); g1.n_experts = shard_n; g1.a_fmt = MX_A_E2M1;
+        g1.s = (const uint8_t*)m->s13; g1.s_estride = (long long)2 * I * (D / 32); g1.s_rstride = D / 32; g1.s_row_shift = 0;
+        g1.N = 2 * I; g1.K = D; g1.x8 = x8s; g1.x8_rows = P; g1.xsf = xsfs; g1.xsf_ld = D / 32;
+        g1.work = work; g1.n_work = n_work; g1.nd = MX_ND_DECODE; g1.rows_a = 32; g1.dual = 1; g1.kb = 4; g1.epi = MX_EPI_SWIGLU_Q8;
+        g1.pair_w = pair_w; g1.out = hq8; g1.out_ld = I; g1.out_sf = hsf; g1.out_sf_ld = I / 32; g1.limit = m->swiglu_limit; g1.inter = I;
+        if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
+        if ((rc = mx_launch(g1, stream))) return rc;
+        if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
+        MxArgs g2{};
+        g2.w = m->w2; g2.w_estride = (long long)D * (I / 2); g2.n_experts = shard_n; g2.a_fmt = MX_A_E2M1;
+        g2.s = (const uint8_t*)m->s2; g2.s_estride = (long long)D * (I / 32); g2.s_rstride = I / 32; g2.s_row_shift = 0;
+        g2.N = D; g2.K = I; g2.x8 = hq8; g2.x8_rows = P; g2.xsf = hsf; g2.xsf_ld = I / 32;
+        g2.work = work; g2.n_work = n_work; g2.nd = MX_ND_DECODE; g2.rows_a = 64; g2.dual = 0; g2.kb = 4; g2.epi = MX_EPI_STORE_F32;
+        g2.pair_out = pair_out; g2.out = y2; g2.out_ld = D;
+        if ((rc = mx_launch(g2, stream))) return rc;
+        if (shared) {
+            MxArgs s1{};
+            s1.w = m->sh_w13; s1.n_experts = 1; s1.a_fmt = MX_A_E4M3;
+            s1.s = (const uint8_t*)m->sh_s13; s1.s_rstride = m->sh_s13_cols; s1.s_row_shift = 5;
+            s1.N = 2 * I; s1.K = D; s1.x8 = x8t; s1.x8_rows = T; s1.xsf = xsft; s1.xsf_ld = D / 32;
+            s1.work = nullptr; s1.dense_rows = T; s1.n_work_host = (T + MX_ND_DECODE - 1) / MX_ND_DECODE;
+            s1.nd = MX_ND_DECODE; s1.rows_a = 32; s1.dual = 1; s1.kb = 4; s1.epi = MX_EPI_SWIGLU_Q8;
+            s1.out = hs8; s1.out_ld = I; s1.out_sf = hssf; s1.out_sf_ld = I / 32; s1.limit = m->swiglu_limit; s1.inter = I; s1.round_gu_bf16 = 1;
+            if ((rc = mx_launch(s1, stream))) return rc;
+            MxArgs s2{};
+            s2.w = m->sh_w2; s2.n_experts = 1; s2.a_fmt = MX_A_E4M3;
+            s2.s = (const uint8_t*)m->sh_s2; s2.s_rstride = m->sh_s2_cols; s2.s_row_shift = 5;
+            s2.N = D; s2.K = I; s2.x8 = hs8; s2.x8_rows = T; s2.xsf = hssf; s2.xsf_ld = I / 32;
+            s2.work = nullptr; s2.dense_rows = T; s2.n_work_host = (T + MX_ND_DECODE - 1) / MX_ND_DECODE;
+            s2.nd = MX_ND_DECODE; s2.rows_a = 64; s2.dual = 0; s2.kb = 4; s2.epi = MX_EPI_STORE_BF16;
+            s2.out = ys; s2.out_ld = D;
+            if ((rc = mx_launch(s2, stream))) return rc;
+        }
+        const long n = (long)T * D;
+        moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y2, eid, shared ? ys : nullptr, (__nv_bfloat16*)m->out, m->routed_out, T, topk, D,
+                                                                           m->shard_start, shard_n);
+        B200_CHECK_LAUNCH();
+        if (m->eid_out && (ce = cudaMemcpyAsync(m->eid_out, eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
+        if (m->wt_out && (ce = cudaMemcpyAsync(m->wt_out, wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
+        return 0;
+    }
     const __nv_bfloat16* xin = m->x_is_quantized ? (const __nv_bfloat16*)m->x : xq;
     const int sbytes = m->expert_fmt == SK_FMT_FP4_BF16S ? 2 : 1;
 
@@ -385,4 +454,51 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         if (ce != cudaSuccess) return (int)ce;
     }
     return 0;
+}
+
+// ------------------------------------------------------------------ block-scaled tensor-core GEMM, stand-alone entry points
+extern "C" int b200_mx_quantize_rows(const void* x, long long x_ld, const int* src_row, int rows, int K, void* q8, void* sf, cudaStream_t stream) {
+    return mx_quantize_rows((const __nv_bfloat16*)x, x_ld, src_row, rows, K, (uint8_t*)q8, (uint8_t*)sf, stream);
+}
+
+extern "C" int b200_device_error(int* code, cudaStream_t stream) {
+    if (!code) return ERR_BAD_ARG;
+    return mx_device_error(code, stream);
+}
+
+extern "C" size_t b200_mx_grouped_workspace_bytes(int n_rows) {
+    if (n_rows < 0) n_rows = 0;
+    return rnd256((size_t)(n_rows + 1) * sizeof(int4)) + 256;
+}
+
+extern "C" int b200_mx_grouped_gemm(const void* w, long long w_estride, const void* s, long long s_estride, int s_cols, int fmt, int n_local_experts, int N,
+                                    int K, const void* x8, long long x8_rows, const void* xsf, const int* grp_expert, const int* grp_start,
+                                    const int* grp_count, int n_groups, const int* pair_out, const float* pair_w, int n_rows, int shard_start,
+                                    int shard_n, int epilogue, float limit, int round_gu_bf16, void* out, long long out_ld, void* out_sf,
+                                    int tokens_per_work, int rows_per_tile, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!w || !s || !x8 || !xsf || !out || n_rows < 0 || n_local_experts < 1) return ERR_BAD_ARG;
+    if (fmt != SK_FMT_FP4_E8M0 && fmt != SK_FMT_FP8_E8M0) return ERR_UNSUPPORTED;
+    if (n_rows == 0) return 0;
+    MxArgs a{};
+    a.w = w; a.w_estride = w_estride; a.n_experts = n_local_experts; a.a_fmt = fmt == SK_FMT_FP4_E8M0 ? MX_A_E2M1 : MX_A_E4M3;
+    a.s = (const uint8_t*)s; a.s_estride = s_estride;
+    a.s_rstride = fmt == SK_FMT_FP4_E8M0 ? K / 32 : s_cols; a.s_row_shift = fmt == SK_FMT_FP4_E8M0 ? 0 : 5;
+    a.N = N; a.K = K; a.x8 = (const uint8_t*)x8; a.x8_rows = x8_rows; a.xsf = (const uint8_t*)xsf; a.xsf_ld = K / 32;
+    a.nd = tokens_per_work; a.rows_a = rows_per_tile; a.kb = 4;
+    a.epi = epilogue; a.dual = epilogue == MX_EPI_SWIGLU_Q8; a.inter = a.dual ? N / 2 : 0; a.limit = limit; a.round_gu_bf16 = round_gu_bf16;
+    a.pair_out = pair_out; a.pair_w = pair_w; a.out = out; a.out_ld = out_ld; a.out_sf = (uint8_t*)out_sf; a.out_sf_ld = a.dual ? N / 2 / 32 : 0;
+    if (grp_expert && n_groups > 0) {
+        if (!grp_start || !workspace || workspace_bytes < b200_mx_grouped_workspace_bytes(n_rows) || ((uintptr_t)workspace & 15)) return ERR_WORKSPACE;
+        Carver cv{(char*)workspace, workspace_bytes};
+        int4* work = cv.take<int4>((size_t)n_rows + 1);
+        int* n_work = cv.take<int>(1);
+        if (!cv.ok) return ERR_WORKSPACE;
+        if (shard_n > n_local_experts) shard_n = n_local_experts;
+        int rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_rows, shard_start, shard_n, work, n_work, n_rows, stream, tokens_per_work);
+        if (rc) return rc;
+        a.work = work; a.n_work = n_work;
+    } else {
+        a.work = nullptr; a.dense_rows = n_rows; a.n_work_host = (n_rows + tokens_per_work - 1) / tokens_per_work;
+    }
+    return mx_launch(a, stream);
 }

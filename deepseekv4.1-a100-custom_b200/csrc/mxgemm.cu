@@ -1,0 +1,448 @@
+// Grouped expert GEMM on the 5th-generation tensor cores with hardware block scaling:
+//     D[weight row, token] = sum_k  W[row, k] * 2^(sw[row, k/32] - 127)  *  q[token, k] * 2^(sx[token, k/32] - 127)
+// W = packed E2M1 (FP4) or e4m3, q = e4m3 activations (the FP8 fake-quantised values of dsv41/quant.py:46-54 kept in
+// quantised form), both with one E8M0 scale byte per 32 k -- exactly the operand formats of
+// tcgen05.mma.kind::mxf8f6f4.block_scale, so the weights go HBM -> TMA -> shared memory -> tensor core with no
+// arithmetic on the way, and the accumulators live in tensor memory (TMEM) in fp32.
+//
+// The weights are the M side of the tile (128 accumulator lanes = weight rows), the tokens of a work (<= nd) are the N side.
+// Warp roles of the persistent CTA:
+//   warp 0      TMA producer: boxes of the weight tile(s) and of the activation rows into a shared-memory ring
+//   warp 1      allocates TMEM; one thread copies the scale atoms into TMEM (tcgen05.cp) and issues the MMAs
+//   warps 4-7   epilogue: tcgen05.ld of the accumulator lanes of their TMEM sub-partition, SwiGLU + FP8 quantisation or store
+//   warps 8-11  scale loaders: one thread per tile row builds the 32x4x4 scale atoms in shared memory
+// Every wait is bounded; a wait that runs out of time records a code in a device error word and the CTA runs to its end.
+//
+// Replaces, on B200, the reference's grouped FP4 kernels (dsv41/moe_kernels.py:341-378 for prefill; dsv41/cuda/fp4_tc.cu,
+// fp4_tcw.cu, expert_chain.cu for decode) when the activation is FP8-quantised, which it always is inside the MoE layer
+// (dsv41/model.py:2040, dsv41/fused.py:297-306).
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "mxgemm.cuh"
+#include "tma.cuh"
+
+namespace b200 {
+
+__device__ int g_mx_error = 0;
+
+// ------------------------------------------------------------------ tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 32 TMEM lanes x 4 columns, replicated into the four sub-partitions
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mx(uint32_t d_taddr, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47, layout type in bits 61-63).
+// K-major operand tile, rows of 128 bytes with the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// scale atom for tcgen05.cp: 32 rows of 16 bytes, no swizzle: 8-row groups are 128 bytes apart
+__device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+// instruction descriptor of kind::mxf8f6f4.block_scale: A format, B = e4m3, both K-major, N, E8M0 scales, M = 128,
+// scale byte j of the 4 in a TMEM column for both operands
+__device__ __forceinline__ uint32_t mx_idesc(int a_fmt, int nd, int j) {
+    return ((uint32_t)j << 4) | ((uint32_t)a_fmt << 7) | (0u << 10) | ((uint32_t)(nd >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24) |
+           ((uint32_t)j << 29);
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(tm), "r"(x),
+                 "r"(y), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// ------------------------------------------------------------------ the kernel
+struct MxSmem {  // offsets inside the 1024-byte aligned dynamic window
+    uint32_t a_tile, b_tile, sf_atom, stage, a_off, b_off, sf_off;
+};
+
+__global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, const __grid_constant__ CUtensorMap tm_a,
+                                                                 const __grid_constant__ CUtensorMap tm_b) {
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    __shared__ __align__(8) unsigned long long bars[3 * MX_MAX_STAGES + 4];  // full_ab[s], full_sf[s], empty[s], acc_full[2], acc_empty[2]
+    __shared__ uint32_t tmem_base_sh;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int NS = a.n_stages, KB = a.kb, nd = a.nd, nt = a.dual ? 2 : 1;
+    uint8_t* base = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+    // stage layout: [tile][kb] A boxes (rows_a x 128 B each), then [kb] B boxes (nd x 128 B)
+    const uint32_t a_box = (uint32_t)a.rows_a * 128u, b_box = (uint32_t)nd * 128u;
+    const uint32_t stage_bytes = (uint32_t)(nt * KB) * a_box + (uint32_t)KB * b_box;  // multiple of 1024 (rows_a, nd multiples of 8)
+    uint8_t* ring = base;
+    uint8_t* sf_ring = base + (size_t)NS * stage_bytes;   // per stage: [kb][nt + 1] atoms of 512 B
+    const uint32_t sf_stage_bytes = (uint32_t)KB * (nt + 1) * 512u;
+    auto bar_full_ab = [&](int s) { return smem_u32(&bars[s]); };
+    auto bar_full_sf = [&](int s) { return smem_u32(&bars[MX_MAX_STAGES + s]); };
+    auto bar_empty = [&](int s) { return smem_u32(&bars[2 * MX_MAX_STAGES + s]); };
+    auto bar_acc_full = [&](int b) { return smem_u32(&bars[3 * MX_MAX_STAGES + b]); };
+    auto bar_acc_empty = [&](int b) { return smem_u32(&bars[3 * MX_MAX_STAGES + 2 + b]); };
+
+    const int kblocks = a.K >> 7;                       // 128-wide k blocks
+    const int spi = (kblocks + KB - 1) / KB;            // stages per item
+    const int rows_item = a.rows_a;                     // weight rows per A tile = output rows (or SwiGLU columns) per item
+    const int n_rows_out = a.dual ? a.inter : a.N;
+    const int ipw = (n_rows_out + rows_item - 1) / rows_item;
+    const int n_work = a.n_work ? *a.n_work : a.n_work_host;
+    const long total = (long)n_work * ipw;
+    const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    const int acc_stride = nt * nd;                     // TMEM columns of one accumulator buffer
+    const int n_acc = (2 * acc_stride <= MX_SF_COL0) ? 2 : 1;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(bar_full_ab(s), 1);
+            mbar_init(bar_full_sf(s), 128);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full(b), 1);
+            mbar_init(bar_acc_empty(b), 128);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_sh), MX_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_sh;
+
+    auto get_work = [&](int wk) -> int4 {
+        if (a.work) return __ldg(a.work + wk);
+        const int rem = a.dense_rows - wk * nd;
+        return make_int4(0, wk * nd, rem < nd ? rem : nd, 0);
+    };
+    const int wk_lo = (int)(lo / ipw), it_lo = (int)(lo - (long)wk_lo * ipw);
+
+    if (lo < hi) {
+        if (warp == 0) {
+            // ------------------------------------------------ TMA producer (one thread)
+            if (lane == 0) {
+                tma_prefetch_desc(&tm_a);
+                tma_prefetch_desc(&tm_b);
+                int wk = wk_lo, it = it_lo;
+                int4 w = get_work(wk);
+                uint32_t n = 0;
+                for (long item = lo; item < hi && !abort_flag; ++item) {
+                    const int row0 = it * rows_item;
+                    for (int st = 0; st < spi; ++st, ++n) {
+                        const uint32_t s = n % NS, ph = (n / NS) & 1;
+                        if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 11)) break;
+                        const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
+                        // packed FP4 boxes are counted by the bytes actually written (8 of every 16-byte slot), not by their footprint
+                        const uint32_t a_tx = a.a_fmt == MX_A_E2M1 ? a_box / 2 : a_box;
+                        mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * ((uint32_t)nt * a_tx + b_box));
+                        const uint32_t dst = smem_u32(ring + (size_t)s * stage_bytes);
+                        for (int b = 0; b < nkb; ++b) {
+                            const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
+                            tma_load_3d(dst + (uint32_t)b * a_box, &tm_a, kx, row0, w.x, bar_full_ab(s));
+                            if (nt == 2) tma_load_3d(dst + (uint32_t)(KB + b) * a_box, &tm_a, kx, a.inter + row0, w.x, bar_full_ab(s));
+                            tma_load_2d(dst + (uint32_t)(nt * KB) * a_box + (uint32_t)b * b_box, &tm_b, kx, w.y, bar_full_ab(s));
+                        }
+                    }
+                    if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
+                }
+                // every load issued above must have landed before the CTA may exit
+                for (int k = 0; k < NS && k < (int)n; ++k) {
+                    const uint32_t m = n - 1 - k, s = m % NS, ph = (m / NS) & 1;
+                    const unsigned long long t0 = global_timer_ns();
+                    while (!mbar_test(bar_full_ab(s), ph)) {
+                        if (global_timer_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(&g_mx_error, 0, 13); break; }
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            // ------------------------------------------------ MMA issuer (one thread)
+            if (lane == 0) {
+                uint32_t n = 0, acc_it = 0;
+                for (long item = lo; item < hi && !abort_flag; ++item, ++acc_it) {
+                    const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
+                    if (!mbar_wait(bar_acc_empty(buf), aph ^ 1, &abort_flag, &g_mx_error, 21)) break;
+                    tc_fence_after();
+                    const uint32_t d0 = tmem_base + buf * acc_stride;
+                    uint32_t accumulate = 0;
+                    for (int st = 0; st < spi; ++st, ++n) {
+                        const uint32_t s = n % NS, ph = (n / NS) & 1;
+                        if (!mbar_wait(bar_full_sf(s), ph, &abort_flag, &g_mx_error, 22)) break;
+                        if (!mbar_wait(bar_full_ab(s), ph, &abort_flag, &g_mx_error, 23)) break;
+                        tc_fence_after();
+                        const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
+                        const uint32_t sbase = smem_u32(ring + (size_t)s * stage_bytes);
+                        const uint32_t sfs = smem_u32(sf_ring + (size_t)s * sf_stage_bytes);
+                        for (int b = 0; b < nkb; ++b) {
+                            // scale atoms of this k block -> TMEM: [A tile 0][A tile 1][B], 4 columns each
+                            const uint32_t sfcol = tmem_base + MX_SF_COL0 + (s * KB + b) * (nt + 1) * 4;
+                            for (int q = 0; q <= nt; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * (nt + 1) + q) * 512u));
+                            const uint64_t da0 = desc_sw128(sbase + (uint32_t)b * a_box);
+                            const uint64_t da1 = desc_sw128(sbase + (uint32_t)(KB + b) * a_box);
+                            const uint64_t db = desc_sw128(sbase + (uint32_t)(nt * KB) * a_box + (uint32_t)b * b_box);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {  // 4 MMAs of K = 32: operand descriptors advance by 32 bytes inside the swizzled row
+                                const uint32_t id = mx_idesc(a.a_fmt, nd, j);
+                                tc_mma_mx(d0, da0 + 2 * j, db + 2 * j, id, sfcol, sfcol + nt * 4, accumulate);
+                                if (nt == 2) tc_mma_mx(d0 + nd, da1 + 2 * j, db + 2 * j, id, sfcol + 4, sfcol + nt * 4, accumulate);
+                                accumulate = 1;
+                            }
+                        }
+                        tc_commit(bar_empty(s));  // the stage (and its scale atoms) may be refilled once these MMAs have read it
+                    }
+                    tc_commit(bar_acc_full(buf));
+                }
+            }
+        } else if (warp >= 8) {
+            // ------------------------------------------------ scale loaders: thread r = accumulator lane r = tile row r
+            const int r = tid - 256;
+            int wk = wk_lo, it = it_lo;
+            int4 w = get_work(wk);
+            uint32_t n = 0;
+            const uint32_t atom_off = (uint32_t)(r & 31) * 16u + (uint32_t)(r >> 5) * 4u;
+            for (long item = lo; item < hi && !abort_flag; ++item) {
+                const int row0 = it * rows_item;
+                const bool arow = r < a.rows_a;
+                const uint8_t* sbase = a.s + (long long)w.x * a.s_estride;
+                const int ra = min(row0 + r, a.N - 1), rb = min(a.inter + row0 + r, a.N - 1);
+                const uint8_t* s_a = sbase + (long)(ra >> a.s_row_shift) * a.s_rstride;
+                const uint8_t* s_b = sbase + (long)(rb >> a.s_row_shift) * a.s_rstride;
+                const bool brow = r < w.z;
+                const uint8_t* s_x = a.xsf + (long)(w.y + (brow ? r : 0)) * a.xsf_ld;
+                for (int st = 0; st < spi; ++st, ++n) {
+                    const uint32_t s = n % NS, ph = (n / NS) & 1;
+                    const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
+                    uint32_t va[4], vb[4], vx[4];
+                    for (int b = 0; b < nkb && b < 4; ++b) {  // issue the loads before waiting for the slot
+                        const int g0 = (kb0 + b) * 4;         // first 32-k group of the k block
+                        va[b] = arow ? ldg_stream4(s_a + g0) : 0x7F7F7F7Fu;
+                        vb[b] = (arow && nt == 2) ? ldg_stream4(s_b + g0) : 0x7F7F7F7Fu;
+                        vx[b] = brow ? ldg_stream4(s_x + g0) : 0x7F7F7F7Fu;
+                    }
+                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 31)) break;
+                    uint8_t* sf = sf_ring + (size_t)s * sf_stage_bytes + atom_off;
+                    for (int b = 0; b < nkb && b < 4; ++b) {
+                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1)) * 512) = va[b];
+                        if (nt == 2) *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + 1) * 512) = vb[b];
+                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + nt) * 512) = vx[b];
+                    }
+                    fence_async_smem();
+                    mbar_arrive(bar_full_sf(s));
+                }
+                if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
+            }
+        } else if (warp >= 4) {
+            // ------------------------------------------------ epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31
+            const int q = warp - 4;
+            const int r = q * 32 + lane;  // tile row
+            int wk = wk_lo, it = it_lo;
+            int4 w = get_work(wk);
+            uint32_t acc_it = 0;
+            for (long item = lo; item < hi && !abort_flag; ++item, ++acc_it) {
+                const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
+                const bool ready = mbar_wait(bar_acc_full(buf), aph, &abort_flag, &g_mx_error, 41);
+                tc_fence_after();
+                const int row0 = it * rows_item;
+                const bool active = (q * 32 < a.rows_a) && ready;  // warp-uniform
+                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
+                for (int c0 = 0; c0 < nd; c0 += 16) {
+                    if (c0 >= w.z) break;  // no tokens in these columns
+                    uint32_t g[16], u[16];
+                    if (active) {
+                        tc_ld16(t0 + c0, g);
+                        if (nt == 2) tc_ld16(t0 + nd + c0, u);
+                        tc_wait_ld();
+                    }
+                    if (!active) continue;
+                    if (a.epi == MX_EPI_SWIGLU_Q8) {
+                        // lane = SwiGLU column row0 + r; the 32 lanes of the warp are one quantisation group (dsv41/fused.py:285-306)
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            if (c0 + c >= w.z) break;
+                            float gt = __uint_as_float(g[c]), up = __uint_as_float(u[c]);
+                            if (a.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
+                            const int prow = w.y + c0 + c;
+                            const float h = swiglu_bf16(gt, up, a.pair_w ? a.pair_w[prow] : 1.f, a.limit);
+                            const float sc = fp8_group_scale(warp_max(fabsf(h)));
+                            const float qv = fminf(fmaxf(__fdiv_rn(h, sc), -448.f), 448.f);
+                            const long orow = a.pair_out ? a.pair_out[prow] : prow;
+                            if (row0 + r < a.inter) {
+                                reinterpret_cast<uint8_t*>(a.out)[orow * a.out_ld + row0 + r] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
+                                if (lane == 0) a.out_sf[orow * a.out_sf_ld + ((row0 + r) >> 5)] = (uint8_t)((f32_as_u32(sc) >> 23) & 0xFFu);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            if (c0 + c >= w.z) break;
+                            const int prow = w.y + c0 + c;
+                            float v = __uint_as_float(g[c]);
+                            if (a.pair_w) v *= a.pair_w[prow];
+                            const long orow = a.pair_out ? a.pair_out[prow] : prow;
+                            if (row0 + r < a.N) {
+                                if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + row0 + r] = v;
+                                else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + row0 + r] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(bar_acc_empty(buf));  // 128 epilogue threads: the accumulator buffer may be overwritten
+                if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, MX_TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ activation quantisation (+ row gather)
+// one warp per (output row, group of 32): q = e4m3(x / s), s = 2^ceil(log2(amax / 448)) (dsv41/quant.py:46-54, quant_fp8)
+__global__ void mx_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const int* __restrict__ src_row, int rows, int K,
+                                        uint8_t* __restrict__ q8, uint8_t* __restrict__ sf) {
+    const long gid = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31, gpr = K >> 5;
+    if (gid >= (long)rows * gpr) return;
+    const int row = (int)(gid / gpr), grp = (int)(gid % gpr);
+    const long src = src_row ? src_row[row] : row;
+    const float v = __bfloat162float(x[src * x_ld + grp * 32 + lane]);
+    const float s = fp8_group_scale(warp_max(fabsf(v)));
+    const float q = fminf(fmaxf(__fdiv_rn(v, s), -448.f), 448.f);
+    q8[(long)row * K + grp * 32 + lane] = (uint8_t)__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
+    if (lane == 0) sf[(long)row * gpr + grp] = (uint8_t)((f32_as_u32(s) >> 23) & 0xFFu);
+}
+
+// ------------------------------------------------------------------ host side
+int sm_count();
+
+static int make_tmap(CUtensorMap* tm, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims, const cuuint64_t* strides,
+                     const cuuint32_t* box) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(tm, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
+    MxArgs a = a_in;
+    if (!a.w || !a.s || !a.x8 || !a.xsf || !a.out) return ERR_BAD_ARG;
+    if (a.a_fmt != MX_A_E2M1 && a.a_fmt != MX_A_E4M3) return ERR_UNSUPPORTED;
+    if (a.K <= 0 || a.K % 128 || a.N <= 0) return ERR_BAD_SHAPE;
+    if (a.nd < 16 || a.nd > 128 || a.nd % 16) return ERR_BAD_SHAPE;
+    if (a.rows_a != 32 && a.rows_a != 64 && a.rows_a != 128) return ERR_BAD_SHAPE;
+    if (a.dual && (a.epi != MX_EPI_SWIGLU_Q8 || a.inter <= 0 || a.inter % 32 || a.N != 2 * a.inter || !a.out_sf)) return ERR_BAD_SHAPE;
+    if (!a.dual && a.epi == MX_EPI_SWIGLU_Q8) return ERR_BAD_SHAPE;
+    if (((uintptr_t)a.w & 31) || (a.w_estride & 31) || ((uintptr_t)a.x8 & 15) || ((uintptr_t)a.s & 3) || (a.s_rstride & 3) || (a.s_estride & 3) ||
+        ((uintptr_t)a.xsf & 3) || (a.xsf_ld & 3))
+        return ERR_BAD_ALIGN;
+    if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
+    const int nt = a.dual ? 2 : 1;
+    if (a.kb < 1 || a.kb > 4) a.kb = 4;
+    const size_t stage = (size_t)(nt * a.kb) * a.rows_a * 128 + (size_t)a.kb * a.nd * 128;
+    const size_t sf_stage = (size_t)a.kb * (nt + 1) * 512;
+    // the A descriptors always span 128 rows: keep 16 KB of slack behind the ring for tiles that fetch fewer rows
+    const size_t slack = 1024 + 16384;
+    int stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
+    if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
+    // scale columns in TMEM: stages * kb * (nt + 1) * 4 <= 256
+    while (stages > 1 && stages * a.kb * (nt + 1) * 4 > MX_TMEM_COLS - MX_SF_COL0) --stages;
+    if (stages < 2) return ERR_BAD_SHAPE;
+    a.n_stages = stages;
+    size_t smem = (size_t)stages * (stage + sf_stage) + slack;
+    if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: each CTA allocates all 512 TMEM columns
+
+    alignas(64) CUtensorMap tm_a, tm_b;
+    const bool fp4 = a.a_fmt == MX_A_E2M1;
+    const uint64_t row_bytes = fp4 ? (uint64_t)a.K / 2 : (uint64_t)a.K;
+    {
+        const uint64_t experts = a.n_experts > 0 ? a.n_experts : 1;
+        cuuint64_t dims[3] = {(cuuint64_t)a.K, (cuuint64_t)a.N, experts};
+        cuuint64_t strides[2] = {row_bytes, (experts == 1 || a.w_estride == 0) ? row_bytes * (uint64_t)a.N : (cuuint64_t)a.w_estride};
+        cuuint32_t box[3] = {128, (cuuint32_t)a.rows_a, 1};
+        int rc = make_tmap(&tm_a, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.w, dims, strides, box);
+        if (rc) return rc;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)(a.x8_rows > 0 ? a.x8_rows : 1)};
+        cuuint64_t strides[1] = {(cuuint64_t)a.K};
+        cuuint32_t box[2] = {128, (cuuint32_t)a.nd};
+        int rc = make_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.x8, dims, strides, box);
+        if (rc) return rc;
+    }
+    static bool attr_done[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(mx_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MX_SMEM_LIMIT);
+        if (e != cudaSuccess) return (int)e;
+        attr_done[dev] = true;
+    }
+    mx_gemm_kernel<<<sm_count(), MX_THREADS, smem, stream>>>(a, tm_a, tm_b);
+    B200_CHECK_LAUNCH();
+    return 0;
+}
+
+int mx_device_error(int* out, cudaStream_t stream) {
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return (int)e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, g_mx_error, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (v) {
+        int z = 0;
+        cudaMemcpyToSymbol(g_mx_error, &z, sizeof(int));
+    }
+    *out = v;
+    return 0;
+}
+
+int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream) {
+    if (!x || !q8 || !sf || rows < 0 || K <= 0 || K % 32) return ERR_BAD_ARG;
+    if (rows == 0) return 0;
+    const long warps = (long)rows * (K / 32);
+    mx_quantize_rows_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf);
+    B200_CHECK_LAUNCH();
+    return 0;
+}
+
+}  // namespace b200

@@ -1,0 +1,63 @@
+// Internal interface of the block-scaled tensor-core grouped GEMM (mxgemm.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int MX_THREADS = 384;   // 12 warps: TMA producer, MMA issuer, 2 spare, 4 epilogue, 4 scale loaders
+constexpr int MX_TMEM_COLS = 512;
+constexpr int MX_SF_COL0 = 256;   // scale factors live in TMEM columns [256, 512)
+constexpr int MX_MAX_STAGES = 8;
+constexpr int MX_SMEM_LIMIT = 227 * 1024 - 2048;
+
+enum { MX_EPI_STORE_F32 = 0, MX_EPI_SWIGLU_Q8 = 1, MX_EPI_STORE_BF16 = 2 };
+enum { MX_A_E4M3 = 0, MX_A_E2M1 = 5 };  // operand format codes of the tensor-core instruction descriptor
+
+struct MxArgs {
+    // A = weights [experts][N rows][K], packed E2M1 (two per byte) or e4m3 bytes
+    const void* w;
+    long long w_estride;    // bytes between experts
+    int n_experts;
+    int a_fmt;              // MX_A_E2M1 / MX_A_E4M3
+    const uint8_t* s;       // E8M0 scale bytes, one per (scale row, 32 k)
+    long long s_estride;    // bytes between experts
+    int s_rstride;          // bytes between scale rows
+    int s_row_shift;        // scale row of weight row r = r >> s_row_shift (0: per row, 5: per 32 rows)
+    int N, K;
+    // B = activations as e4m3 bytes [rows][K] with E8M0 scale bytes [rows][K/32]
+    const uint8_t* x8;
+    long long x8_rows;      // rows the buffer holds (bound of the tensor map)
+    const uint8_t* xsf;
+    int xsf_ld;
+    // works: {local expert, first B row, rows (1..nd), -}; nullptr = dense mode over dense_rows rows, expert 0
+    const int4* work;
+    const int* n_work;
+    int n_work_host;
+    int dense_rows;
+    int nd;                 // token columns per work = N of the tensor-core tile (multiple of 16, <= 128)
+    int rows_a;             // weight rows fetched per A tile (32, 64 or 128); the tile always spans 128 accumulator lanes
+    int dual;               // 1: two A tiles per item (gate rows r and up rows inter + r), epilogue SWIGLU
+    int kb;                 // 128-wide k blocks per pipeline stage
+    int n_stages;
+    int epi;
+    const int* pair_out;    // output row of B row p (nullptr: p)
+    const float* pair_w;    // optional weight per B row
+    void* out;              // f32 / bf16 [rows][N] or, for SWIGLU, e4m3 bytes [rows][inter]
+    long long out_ld;
+    uint8_t* out_sf;        // SWIGLU: E8M0 scale bytes [rows][inter/32]
+    int out_sf_ld;
+    float limit;
+    int inter;
+    int round_gu_bf16;
+};
+
+int mx_launch(const MxArgs& a, cudaStream_t stream);
+int mx_device_error(int* out, cudaStream_t stream);  // copies and clears the device error word (synchronises the stream)
+
+// bf16 [rows][K] -> e4m3 bytes + E8M0 scale byte per 32 (the FP8 fake quantisation of dsv41/quant.py:46-54 kept in
+// quantised form); optional row gather: output row p reads input row src_row[p]
+int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream);
+
+}  // namespace b200

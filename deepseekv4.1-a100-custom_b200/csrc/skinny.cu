@@ -415,7 +415,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
 // groups, expert -1) get their output rows zeroed when zero_out is set, as dsv41/cuda/fp4_tc.cu:66-72 does.
 __global__ void __launch_bounds__(1024) skinny_plan_kernel(const int* __restrict__ grp_expert, const int* __restrict__ grp_start,
                                                            const int* __restrict__ grp_count, int G, int n_pairs, int shard_start, int shard_n,
-                                                           int4* __restrict__ work, int* __restrict__ n_work, int max_work) {
+                                                           int4* __restrict__ work, int* __restrict__ n_work, int max_work, int tpw) {
     __shared__ int warp_tot[32];
     __shared__ int running;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -430,7 +430,7 @@ __global__ void __launch_bounds__(1024) skinny_plan_kernel(const int* __restrict
             int en = grp_count ? s + grp_count[gi] : grp_start[gi + 1];
             if (en > n_pairs) en = n_pairs;
             cnt = en - s;
-            if (e >= 0 && e < shard_n && cnt > 0 && s >= 0) nsub = (cnt + SK_TOK - 1) / SK_TOK;
+            if (e >= 0 && e < shard_n && cnt > 0 && s >= 0) nsub = (cnt + tpw - 1) / tpw;
         }
         int incl = nsub;
 #pragma unroll
@@ -446,8 +446,8 @@ __global__ void __launch_bounds__(1024) skinny_plan_kernel(const int* __restrict
         for (int w = 0; w < 32; ++w) tot += warp_tot[w];
         const int off = running + woff + incl - nsub;
         for (int i = 0; i < nsub; ++i) {
-            const int rem = cnt - i * SK_TOK;
-            if (off + i < max_work) work[off + i] = make_int4(e, s + i * SK_TOK, rem < SK_TOK ? rem : SK_TOK, gi);
+            const int rem = cnt - i * tpw;
+            if (off + i < max_work) work[off + i] = make_int4(e, s + i * tpw, rem < tpw ? rem : tpw, gi);
         }
         __syncthreads();
         if (tid == 0) running += tot;
@@ -547,8 +547,8 @@ int skinny_launch(const SkinnyArgs& a_in, int fmt, int epi, cudaStream_t stream)
 }
 
 int skinny_plan(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n, int4* work,
-                int* n_work, int max_work, cudaStream_t stream) {
-    skinny_plan_kernel<<<1, 1024, 0, stream>>>(grp_expert, grp_start, grp_count, G, n_pairs, shard_start, shard_n, work, n_work, max_work);
+                int* n_work, int max_work, cudaStream_t stream, int tpw) {
+    skinny_plan_kernel<<<1, 1024, 0, stream>>>(grp_expert, grp_start, grp_count, G, n_pairs, shard_start, shard_n, work, n_work, max_work, tpw);
     B200_CHECK_LAUNCH();
     return 0;
 }

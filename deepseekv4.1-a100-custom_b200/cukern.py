@@ -158,3 +158,70 @@ def p2p_sum_rows(dst: torch.Tensor, src: torch.Tensor, device: torch.device, gro
     assert src.dtype == torch.float32 and dst.dtype == torch.float32 and src.is_contiguous()
     with torch.cuda.device(device):
         L.check(L.lib().b200_sum_rows(L.ptr(dst), L.ptr(src), rows, n, groups, int(dst_stride), L.stream_of(device)), "b200_sum_rows")
+
+
+# --------------------------------------------------------------------------- block-scaled tensor-core path (FP8 activations)
+def mx_quantize_rows(x: torch.Tensor, src_row: torch.Tensor | None = None):
+    """bf16 [rows_in, K] -> (q8 uint8 e4m3 [rows, K], sf uint8 E8M0 [rows, K/32]); src_row int32 [rows] gathers input rows.
+    q8 * 2^(sf - 127) equals fake_quant_fp8(x) (dsv41/quant.py:46-64)."""
+    dev = L.require_cuda(x, src_row)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] % 32 == 0
+    K = x.shape[1]
+    sr = _i32(src_row, dev)
+    rows = sr.numel() if sr is not None else x.shape[0]
+    q8 = torch.empty(rows + 128, K, device=dev, dtype=torch.uint8)[:rows]  # slack rows: tensor-map boxes may read past the last work
+    sf = torch.empty(rows + 128, K // 32, device=dev, dtype=torch.uint8)[:rows]
+    with torch.cuda.device(dev):
+        L.check(L.lib().b200_mx_quantize_rows(L.ptr(x), x.stride(0), L.ptr(sr), rows, K, L.ptr(q8), L.ptr(sf), L.stream_of(dev)), "b200_mx_quantize_rows")
+    return q8, sf
+
+
+def mx_grouped(w, s, x8, xsf, grp_expert, grp_start, grp_count, pair_out, pair_w, n_rows, *, epilogue="f32", limit=0.0, round_gu_bf16=False,
+               shard_start=0, shard_n=1 << 30, tokens_per_work=16, rows_per_tile=32, out=None, n_out_rows=None):
+    """Launcher of b200_mx_grouped_gemm (include/b200_moe.h).  w uint8 [E, N, K/2] + s uint8 [E, N, K/32] (FP4) or w uint8 e4m3
+    [N, K] natural k order + s uint8 [ceil(N/32), K/32] (FP8, grp_expert = None: every row against the one matrix)."""
+    dev = L.require_cuda(w, s, x8, xsf, out)
+    fp4 = w.dim() == 3
+    if fp4:
+        E, N, Kh = w.shape
+        K = Kh * 2
+        fmt, s_cols = L.FMT_FP4_E8M0, K // 32
+        w_es, s_es = w.stride(0), s.stride(0)
+    else:
+        N, K = w.shape
+        E, fmt, s_cols, w_es, s_es = 1, L.FMT_FP8_E8M0, s.shape[1], 0, 0
+    assert w.is_contiguous() and s.is_contiguous() and x8.dtype == torch.uint8 and x8.shape[1] == K and x8.is_contiguous() and xsf.is_contiguous()
+    epi = {"f32": 0, "swiglu_q8": 1, "bf16": 2}[epilogue]
+    rows_out = n_rows if n_out_rows is None else n_out_rows
+    out_sf = None
+    if out is None:
+        if epi == 1:
+            out = torch.empty(rows_out + 128, N // 2, device=dev, dtype=torch.uint8)[:rows_out]
+            out_sf = torch.empty(rows_out + 128, N // 64, device=dev, dtype=torch.uint8)[:rows_out]
+        else:
+            out = torch.empty(rows_out, N, device=dev, dtype=torch.float32 if epi == 0 else torch.bfloat16)
+    elif epi == 1:
+        out, out_sf = out
+    ge, gs, gc = _i32(grp_expert, dev), _i32(grp_start, dev), _i32(grp_count, dev)
+    po = _i32(pair_out, dev)
+    pw = pair_w.to(device=dev, dtype=torch.float32).contiguous() if pair_w is not None else None
+    lib = L.lib()
+    ws = L.workspace(dev, lib.b200_mx_grouped_workspace_bytes(int(n_rows)), "mx_grouped")
+    # the tensor map is bounded by the rows the underlying buffer really holds
+    x8_rows = x8.untyped_storage().nbytes() // K if x8.storage_offset() == 0 else x8.shape[0]
+    with torch.cuda.device(dev):
+        rc = lib.b200_mx_grouped_gemm(L.ptr(w), w_es, L.ptr(s), s_es, s_cols, fmt, E, N, K, L.ptr(x8), x8_rows, L.ptr(xsf), L.ptr(ge), L.ptr(gs), L.ptr(gc),
+                                      ge.numel() if ge is not None else 0, L.ptr(po), L.ptr(pw), int(n_rows), int(shard_start), int(min(shard_n, 1 << 30)), epi,
+                                      float(limit), int(bool(round_gu_bf16)), L.ptr(out), out.stride(0), L.ptr(out_sf), int(tokens_per_work), int(rows_per_tile),
+                                      L.ptr(ws), ws.numel(), L.stream_of(dev))
+    L.check(rc, "b200_mx_grouped_gemm")
+    return (out, out_sf) if epi == 1 else out
+
+
+def device_error(device) -> int:
+    """Synchronise the device's current stream and return (then clear) the device error word (0 = no bounded wait gave up)."""
+    import ctypes
+    code = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        L.check(L.lib().b200_device_error(ctypes.byref(code), L.stream_of(device)), "b200_device_error")
+    return code.value

@@ -147,10 +147,40 @@ typedef struct b200_moe_args {
      * gate/up weight stream), so that a benchmark can time that kernel alone; NULL = not recorded */
     void* prof_start;
     void* prof_stop;
+    /* 0 = automatic, 1 = weight-streaming path with in-register dequantisation (any scale format), 2 = block-scaled
+     * tensor-core path (tcgen05 kind::mxf8f6f4; needs E8M0 scales and the shared expert in natural k order, sh_permk = 0) */
+    int engine;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);
 int b200_moe_forward(const b200_moe_args* args, cudaStream_t stream);
+
+/* ---- FP8 quantisation of activation rows kept in quantised form: q8 e4m3 [rows, K], sf E8M0 bytes [rows, K/32], the
+ * values of quant_fp8 (dsv41/quant.py:57-64).  src_row int32 [rows] gathers input rows (NULL = identity). */
+int b200_mx_quantize_rows(const void* x, long long x_ld, const int* src_row, int rows, int K, void* q8, void* sf, cudaStream_t stream);
+
+/* ---- grouped expert GEMM on the block-scaled tensor cores (tcgen05.mma kind::mxf8f6f4, TMA, TMEM).  Same group / shard
+ * contract as b200_fp4_grouped_gemm, but the activation arrives FP8-quantised (x8 e4m3 [x8_rows, K] + xsf E8M0 [x8_rows, K/32];
+ * row p of x8 is pair p, i.e. already gathered into pair order), which is what the MoE layer feeds its experts
+ * (dsv41/model.py:2040, dsv41/fused.py:297-306).  Replaces grouped_fp4_gemm (dsv41/moe_kernels.py:161-231) and fp4_gemm_tc
+ * (dsv41/cukern.py:309-344) on that path, and linear_w (dsv41/w8.py:64-83) for the shared expert (fmt B200_FMT_FP8_E8M0, weight
+ * bytes in NATURAL k order, n_groups = 0: every row of x8 against the single matrix).
+ *   epilogue 0: out fp32 [.., N] = rows of x8 @ W^T (times pair_w);  2: the same rounded to bf16;
+ *   epilogue 1: N = 2*inter, out e4m3 [.., inter] + out_sf E8M0 [.., inter/32] = FP8 quantisation of
+ *               bf16(pair_w * silu(min(g, limit)) * clamp(u, +-limit)), g = rows 0..inter-1, u = rows inter..2*inter-1
+ *               (dsv41/fused.py:285-306); round_gu_bf16 rounds g, u to bf16 first (shared expert).
+ *   tokens_per_work: 16..128, multiple of 16 (N of the tensor-core tile); rows_per_tile: 32, 64 or 128 weight rows per tile.
+ *   K % 128 == 0; w 32-byte aligned; workspace b200_mx_grouped_workspace_bytes(n_rows) bytes when groups are given. */
+size_t b200_mx_grouped_workspace_bytes(int n_rows);
+int b200_mx_grouped_gemm(const void* w, long long w_estride, const void* s, long long s_estride, int s_cols, int fmt, int n_local_experts, int N, int K,
+                         const void* x8, long long x8_rows, const void* xsf, const int* grp_expert, const int* grp_start, const int* grp_count,
+                         int n_groups, const int* pair_out, const float* pair_w, int n_rows, int shard_start, int shard_n, int epilogue, float limit,
+                         int round_gu_bf16, void* out, long long out_ld, void* out_sf, int tokens_per_work, int rows_per_tile, void* workspace,
+                         size_t workspace_bytes, cudaStream_t stream);
+
+/* ---- device error word.  Every device-side wait of this library is bounded; one that runs out of time stores a non-zero
+ * code instead of hanging.  Synchronises `stream`, returns the code in *code (0 = none) and clears it. */
+int b200_device_error(int* code, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

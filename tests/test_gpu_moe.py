@@ -8,7 +8,7 @@ from conftest import rel_err
 pytestmark = pytest.mark.gpu
 
 
-def _layer(mods, dev, E, D, I, topk, seed, kind="e8m0", lo=123, hi=130, limit=10.0, shard=None, bf16_scales=False):
+def _layer(mods, dev, E, D, I, topk, seed, kind="e8m0", lo=123, hi=130, limit=10.0, shard=None, bf16_scales=False, engine=0):
     ex = mods.synth.make_experts(E, D, I, seed=seed, scale_lo=lo, scale_hi=hi)
     sh = mods.synth.make_shared(D, I, seed=seed + 1, kind=kind)
     start, n = shard or (0, E)
@@ -16,7 +16,7 @@ def _layer(mods, dev, E, D, I, topk, seed, kind="e8m0", lo=123, hi=130, limit=10
     conv = (lambda t: mods.synth.e8m0_to_bf16(t)) if bf16_scales else (lambda t: t)
     layer = mods.moe.MoELayer(ex["w13"][sl].to(dev), conv(ex["s13"][sl]).to(dev), ex["w2"][sl].to(dev), conv(ex["s2"][sl]).to(dev), n_experts=E, topk=topk,
                               sh_w13=mods.w8.W8(sh["w13"].to(dev), sh["s13"].to(dev)), sh_w2=mods.w8.W8(sh["w2"].to(dev), sh["s2"].to(dev)),
-                              swiglu_limit=limit, shard_start=start)
+                              swiglu_limit=limit, shard_start=start, engine=engine)
     return ex, sh, layer
 
 
@@ -35,9 +35,11 @@ def _check(mods, oracle, dev, E, D, I, topk, T, seed, **kw):
     return rel_err(out, ref["out"])
 
 
+@pytest.mark.parametrize("engine", [1, 2])
 @pytest.mark.parametrize("T", [1, 2, 8, 9, 33, 64])
-def test_layer_small_dims(mods, oracle, dev, T):
-    _check(mods, oracle, dev, E=16, D=512, I=256, topk=4, T=T, seed=10 + T, lo=116, hi=122)
+def test_layer_small_dims(mods, oracle, dev, T, engine):
+    _check(mods, oracle, dev, E=16, D=512, I=256, topk=4, T=T, seed=10 + T, lo=116, hi=122, engine=engine)
+    assert mods.cukern.device_error(dev) == 0
 
 
 @pytest.mark.parametrize("T", [1, 8])
@@ -48,6 +50,9 @@ def test_layer_full_dims(mods, oracle, dev, T, setting):
     kw = {"saturated": dict(lo=123, hi=130), "unsaturated": dict(lo=112, hi=120), "noclamp": dict(lo=112, hi=120, limit=0.0),
           "f32b": dict(lo=112, hi=120, kind="f32b")}[setting]
     _check(mods, oracle, dev, E=24, D=4096, I=2048, topk=6, T=T, seed=50 + T, **kw)
+    assert mods.cukern.device_error(dev) == 0
+    if setting != "f32b":  # the streaming engine on the same inputs
+        _check(mods, oracle, dev, E=24, D=4096, I=2048, topk=6, T=T, seed=50 + T, engine=1, **kw)
 
 
 def test_layer_bf16_scales_equal_e8m0(mods, dev):
