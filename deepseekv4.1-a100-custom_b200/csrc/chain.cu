@@ -34,6 +34,7 @@ struct RouteArgs {
     int4* work;
     int* n_work;
     unsigned int* counter;
+    int no_bucket;      // 1: only quantise + route; the pairs are bucketed by the multi-block kernels below
 };
 
 // One block per token: fake-quantise the token's activation (dsv41/quant.py:46-54; one thread per group of 32, four 16-byte
@@ -77,6 +78,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
     }
     gate_topk_row(a.logits_f32 ? a.logits_f32 + (long)tok * a.E : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.E : nullptr, a.bias, a.E,
                   a.temp, a.topk, a.route_scale, a.mode, a.norm, a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, sh_f, sh_i);
+    if (a.no_bucket) return;
     __threadfence();
     __syncthreads();
     if (tid == 0) is_last = (atomicInc(a.counter, gridDim.x - 1) == gridDim.x - 1);
@@ -153,6 +155,60 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
             }
         }
     }
+}
+
+// ------------------------------------------------------------------ bucketing of many pairs (prefill): histogram, scan + work list, scatter.
+// The order of the pairs inside an expert is whatever the atomic cursors give: every pair is computed independently and the
+// per-token sum is formed elsewhere, so the order does not reach the results.
+__global__ void pair_hist_kernel(const int* __restrict__ eid, int P, int* __restrict__ cnt) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p < P) atomicAdd(cnt + eid[p], 1);
+}
+
+__global__ void __launch_bounds__(1024) pair_scan_kernel(const int* __restrict__ cnt, int E, int shard_start, int shard_n, int tpw, int* __restrict__ cursor,
+                                                         int4* __restrict__ work, int* __restrict__ n_work) {
+    __shared__ int wp[32], ww[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int c = tid < E ? cnt[tid] : 0;
+    const bool mine = tid < E && tid >= shard_start && tid < shard_start + shard_n;
+    const int nw = mine ? (c + tpw - 1) / tpw : 0;
+    int ip = c, iw = nw;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int vp = __shfl_up_sync(0xffffffffu, ip, o), vw = __shfl_up_sync(0xffffffffu, iw, o);
+        if (lane >= o) { ip += vp; iw += vw; }
+    }
+    if (lane == 31) { wp[warp] = ip; ww[warp] = iw; }
+    __syncthreads();
+    int bp = ip - c, bw = iw - nw, tw = 0;
+    for (int w = 0; w < 32; ++w) {
+        if (w < warp) { bp += wp[w]; bw += ww[w]; }
+        tw += ww[w];
+    }
+    if (tid < E) {
+        cursor[tid] = bp;
+        for (int i = 0; i < nw; ++i) {
+            const int rem = c - i * tpw;
+            work[bw + i] = make_int4(tid - shard_start, bp + i * tpw, rem < tpw ? rem : tpw, tid);
+        }
+    }
+    if (tid == 0) *n_work = tw;
+}
+
+__global__ void pair_scatter_kernel(const int* __restrict__ eid, const float* __restrict__ wt, int P, int topk, int* __restrict__ cursor,
+                                    int* __restrict__ pair_tok, int* __restrict__ pair_out, float* __restrict__ pair_w, int out_is_token) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= P) return;
+    const int pos = atomicAdd(cursor + eid[p], 1);
+    pair_tok[pos] = p / topk;
+    pair_out[pos] = out_is_token ? p / topk : p;
+    pair_w[pos] = wt[p];
+}
+
+// out[t, n] = bf16(acc[t, n] + float(ys[t, n]))
+__global__ void moe_finalize_kernel(const float* __restrict__ acc, const __nv_bfloat16* __restrict__ ys, __nv_bfloat16* __restrict__ out, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2bfloat16_rn(acc[i] + (ys ? __bfloat162float(ys[i]) : 0.f));
 }
 
 // out[t, n] = bf16( sum over the token's LOCAL experts of y2[t*topk + j, n] + float(ys[t, n]) )  (dsv41/fused2.py:518-523);
@@ -271,25 +327,50 @@ extern "C" int b200_fp8_gemm(const void* x, long long x_ld, int M, const void* w
 }
 
 // ------------------------------------------------------------------ whole layer
+// Workspace of one layer call, carved identically by b200_moe_workspace_bytes and b200_moe_forward.
+struct MoeWs {
+    __nv_bfloat16* xq; int* eid; float* wt; int* pair_tok; int* pair_out; float* pair_w; int4* work; int* n_work; unsigned int* counter;
+    int* cnt; int* cursor; __nv_bfloat16* hq; __nv_bfloat16* hs; float* y2; float* acc; __nv_bfloat16* ys;
+    uint8_t *x8s, *xsfs, *x8t, *xsft, *hq8, *hsf, *hs8, *hssf;
+};
+
+static bool carve_moe(Carver& cv, MoeWs& w, int T, int topk, int D, int I) {
+    const size_t P = (size_t)T * topk;
+    const bool small = P <= (size_t)ROUTE_MAX_PAIRS;  // decode-sized batches keep bf16 intermediates for the streaming engine
+    w.xq = cv.take<__nv_bfloat16>(small ? (size_t)T * D : 0);
+    w.eid = cv.take<int>(P);
+    w.wt = cv.take<float>(P);
+    w.pair_tok = cv.take<int>(P);
+    w.pair_out = cv.take<int>(P);
+    w.pair_w = cv.take<float>(P);
+    w.work = cv.take<int4>(P + 1);
+    w.n_work = cv.take<int>(1);
+    w.counter = cv.take<unsigned int>(1);
+    w.cnt = cv.take<int>(ROUTE_MAX_EXPERTS);
+    w.cursor = cv.take<int>(ROUTE_MAX_EXPERTS);
+    w.hq = cv.take<__nv_bfloat16>(small ? P * I : 0);
+    w.hs = cv.take<__nv_bfloat16>(small ? (size_t)T * I : 0);
+    w.y2 = cv.take<float>(small ? P * D : 0);          // per-pair results (summed in slot order: deterministic)
+    w.acc = cv.take<float>(small ? 0 : (size_t)T * D);  // per-token accumulator of the prefill path
+    w.ys = cv.take<__nv_bfloat16>((size_t)T * D);
+    // activations as e4m3 bytes + E8M0 scale bytes; 128 slack rows: tensor-map boxes of the last work may read past the end
+    w.x8s = cv.take<uint8_t>((P + 128) * D);
+    w.xsfs = cv.take<uint8_t>((P + 128) * (D / 32));
+    w.x8t = cv.take<uint8_t>(((size_t)T + 128) * D);
+    w.xsft = cv.take<uint8_t>(((size_t)T + 128) * (D / 32));
+    w.hq8 = cv.take<uint8_t>((P + 128) * I);
+    w.hsf = cv.take<uint8_t>((P + 128) * (I / 32));
+    w.hs8 = cv.take<uint8_t>(((size_t)T + 128) * I);
+    w.hssf = cv.take<uint8_t>(((size_t)T + 128) * (I / 32));
+    return cv.ok;
+}
+
 extern "C" size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter) {
     if (tokens < 0 || topk < 0 || dim < 0 || inter < 0) return 0;
-    const size_t P = (size_t)tokens * topk;
-    size_t b = 0;
-    b += rnd256((size_t)tokens * dim * 2);  // xq
-    b += rnd256(P * 4) * 2;                 // eid, wt
-    b += rnd256(P * 4) * 3;                 // pair_tok, pair_out, pair_w
-    b += rnd256((P + 1) * 16);              // work
-    b += rnd256(4) * 2;                     // n_work, counter
-    b += rnd256(P * inter * 2);             // hq
-    b += rnd256((size_t)tokens * inter * 2);  // hs
-    b += rnd256(P * dim * 4);               // y2
-    b += rnd256((size_t)tokens * dim * 2);  // ys
-    // block-scaled tensor-core path: activations as e4m3 bytes + E8M0 scale bytes
-    b += rnd256((P + 128) * dim) + rnd256((P + 128) * (dim / 32));                          // x8s, xsfs (pair-sorted gather)
-    b += rnd256(((size_t)tokens + 128) * dim) + rnd256(((size_t)tokens + 128) * (dim / 32));    // x8t, xsft
-    b += rnd256((P + 128) * inter) + rnd256((P + 128) * (inter / 32));                      // hq8, hsf
-    b += rnd256(((size_t)tokens + 128) * inter) + rnd256(((size_t)tokens + 128) * (inter / 32));  // hs8, hssf
-    return b + 256;
+    Carver cv{nullptr, (size_t)1 << 62};
+    MoeWs w;
+    carve_moe(cv, w, tokens, topk, dim, inter);
+    return (size_t)(cv.p - (char*)nullptr) + 256;
 }
 
 extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
@@ -299,7 +380,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->tokens == 0) return 0;
     const int T = m->tokens, topk = m->topk, D = m->dim, I = m->inter, E = m->n_experts;
     const long P = (long)T * topk;
-    if (P > ROUTE_MAX_PAIRS || E > ROUTE_MAX_EXPERTS || topk > 32 || topk > E) return ERR_BAD_SHAPE;
+    if (P > (1L << 30) || E > ROUTE_MAX_EXPERTS || topk > 32 || topk > E) return ERR_BAD_SHAPE;
     if (D % 128 || I % 128) return ERR_BAD_SHAPE;
     if (m->expert_fmt != SK_FMT_FP4_E8M0 && m->expert_fmt != SK_FMT_FP4_BF16S) return ERR_UNSUPPORTED;
     if (m->has_shared && m->shared_fmt != SK_FMT_FP8_E8M0 && m->shared_fmt != SK_FMT_FP8_F32B) return ERR_UNSUPPORTED;
@@ -309,150 +390,142 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->shard_start < 0 || shard_n < 1 || shard_n > E) return ERR_BAD_ARG;
 
     Carver cv{(char*)m->workspace, m->workspace_bytes};
-    __nv_bfloat16* xq = cv.take<__nv_bfloat16>((size_t)T * D);
-    int* eid = cv.take<int>(P);
-    float* wt = cv.take<float>(P);
-    int* pair_tok = cv.take<int>(P);
-    int* pair_out = cv.take<int>(P);
-    float* pair_w = cv.take<float>(P);
-    int4* work = cv.take<int4>(P + 1);
-    int* n_work = cv.take<int>(1);
-    unsigned int* counter = cv.take<unsigned int>(1);
-    __nv_bfloat16* hq = cv.take<__nv_bfloat16>((size_t)P * I);
-    __nv_bfloat16* hs = cv.take<__nv_bfloat16>((size_t)T * I);
-    float* y2 = cv.take<float>((size_t)P * D);
-    __nv_bfloat16* ys = cv.take<__nv_bfloat16>((size_t)T * D);
-    uint8_t* x8s = cv.take<uint8_t>((size_t)(P + 128) * D);
-    uint8_t* xsfs = cv.take<uint8_t>((size_t)(P + 128) * (D / 32));
-    uint8_t* x8t = cv.take<uint8_t>((size_t)(T + 128) * D);
-    uint8_t* xsft = cv.take<uint8_t>((size_t)(T + 128) * (D / 32));
-    uint8_t* hq8 = cv.take<uint8_t>((size_t)(P + 128) * I);
-    uint8_t* hsf = cv.take<uint8_t>((size_t)(P + 128) * (I / 32));
-    uint8_t* hs8 = cv.take<uint8_t>((size_t)(T + 128) * I);
-    uint8_t* hssf = cv.take<uint8_t>((size_t)(T + 128) * (I / 32));
-    if (!cv.ok) return ERR_WORKSPACE;
-    // engine: 1 = streaming bf16 path (any scale format), 2 = block-scaled tensor cores (E8M0 scales, natural k order of the
-    // shared expert); 0 = choose 2 when the formats allow it
-    const bool mx_ok = m->expert_fmt == SK_FMT_FP4_E8M0 && (!m->has_shared || (m->shared_fmt == SK_FMT_FP8_E8M0 && !m->sh_permk)) && D % 128 == 0 && I % 128 == 0;
-    if (m->engine == 2 && !mx_ok) return ERR_UNSUPPORTED;
-    const bool use_mx = m->engine == 2 || (m->engine == 0 && mx_ok);
+    MoeWs w;
+    if (!carve_moe(cv, w, T, topk, D, I)) return ERR_WORKSPACE;
+    const bool small = P <= ROUTE_MAX_PAIRS;
+    // engine: 1 = weight streaming with in-register dequantisation (any scale format, decode-sized batches only),
+    //         2 = block-scaled tensor cores (E8M0 scales, natural k order of the shared expert), 0 = automatic:
+    //         streaming for decode-sized batches (<= 64 tokens), tensor cores beyond
+    const bool mx_ok = m->expert_fmt == SK_FMT_FP4_E8M0 && (!m->has_shared || (m->shared_fmt == SK_FMT_FP8_E8M0 && !m->sh_permk));
+    if ((m->engine == 2 || !small) && !mx_ok) return ERR_UNSUPPORTED;
+    if (m->engine == 1 && !small) return ERR_UNSUPPORTED;
+    const bool use_mx = m->engine == 2 || !small || (m->engine == 0 && mx_ok && T > 64);
+    const bool shared = m->has_shared && m->out;
+    cudaError_t ce;
+    int rc;
 
-    // the counter of the "last block" election must start at zero; it resets itself after every launch
-    cudaError_t ce = cudaMemsetAsync(counter, 0, sizeof(unsigned int), stream);
-    if (ce != cudaSuccess) return (int)ce;
-
+    // ---- routing (+ bf16 fake quantisation of the input for the streaming engine)
     RouteArgs r{};
     r.tokens = T; r.E = E; r.topk = topk; r.dim = D;
     r.logits_f32 = m->logits_is_bf16 ? nullptr : (const float*)m->logits;
     r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
     r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
-    r.x = (const __nv_bfloat16*)m->x; r.xq = (m->x_is_quantized || use_mx) ? nullptr : xq;
-    r.shard_start = m->shard_start; r.shard_n = shard_n; r.tpw = use_mx ? MX_ND_DECODE : SK_TOK;
-    r.eid = eid; r.wt = wt; r.pair_tok = pair_tok; r.pair_out = pair_out; r.pair_w = pair_w; r.work = work; r.n_work = n_work; r.counter = counter;
+    r.x = (const __nv_bfloat16*)m->x; r.xq = (m->x_is_quantized || use_mx) ? nullptr : w.xq;
+    r.shard_start = m->shard_start; r.shard_n = shard_n;
+    const int nd = small ? MX_ND_DECODE : 128;  // token columns per work of the tensor-core path
+    r.tpw = use_mx ? nd : SK_TOK;
+    r.eid = w.eid; r.wt = w.wt; r.pair_tok = w.pair_tok; r.pair_out = w.pair_out; r.pair_w = w.pair_w; r.work = w.work; r.n_work = w.n_work;
+    r.counter = w.counter; r.no_bucket = small ? 0 : 1;
+    if (small) {  // the counter of the "last block" election starts at zero and resets itself after every launch
+        if ((ce = cudaMemsetAsync(w.counter, 0, sizeof(unsigned int), stream)) != cudaSuccess) return (int)ce;
+    }
     moe_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
     B200_CHECK_LAUNCH();
+    if (!small) {  // many pairs: multi-block histogram / scan / scatter; GEMM-2 adds into a per-token accumulator
+        if ((ce = cudaMemsetAsync(w.cnt, 0, sizeof(int) * ROUTE_MAX_EXPERTS, stream)) != cudaSuccess) return (int)ce;
+        if ((ce = cudaMemsetAsync(w.acc, 0, sizeof(float) * (size_t)T * D, stream)) != cudaSuccess) return (int)ce;
+        pair_hist_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(w.eid, (int)P, w.cnt);
+        B200_CHECK_LAUNCH();
+        pair_scan_kernel<<<1, 1024, 0, stream>>>(w.cnt, E, m->shard_start, shard_n, nd, w.cursor, w.work, w.n_work);
+        B200_CHECK_LAUNCH();
+        pair_scatter_kernel<<<(unsigned)((P + 255) / 256), 256, 0, stream>>>(w.eid, w.wt, (int)P, topk, w.cursor, w.pair_tok, w.pair_out, w.pair_w, 1);
+        B200_CHECK_LAUNCH();
+    }
+
     if (use_mx) {
-        const bool shared = m->has_shared && m->out;
         // activations -> e4m3 + E8M0 (the FP8 fake quantisation kept in quantised form), gathered into pair-sorted order
-        int rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, pair_tok, (int)P, D, x8s, xsfs, stream);
-        if (rc) return rc;
-        if (shared && (rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, nullptr, T, D, x8t, xsft, stream))) return rc;
+        if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream))) return rc;
+        if (shared && (rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, nullptr, T, D, w.x8t, w.xsft, stream))) return rc;
+        const int rows1 = small ? 32 : 128, rows2 = small ? 64 : 128;
         MxArgs g1{};
         g1.w = m->w13; g1.w_estride = (long long)2 * I * (D / 2); g1.n_experts = shard_n; g1.a_fmt = MX_A_E2M1;
         g1.s = (const uint8_t*)m->s13; g1.s_estride = (long long)2 * I * (D / 32); g1.s_rstride = D / 32; g1.s_row_shift = 0;
-        g1.N = 2 * I; g1.K = D; g1.x8 = x8s; g1.x8_rows = P; g1.xsf = xsfs; g1.xsf_ld = D / 32;
-        g1.work = work; g1.n_work = n_work; g1.nd = MX_ND_DECODE; g1.rows_a = 32; g1.dual = 1; g1.kb = 4; g1.epi = MX_EPI_SWIGLU_Q8;
-        g1.pair_w = pair_w; g1.out = hq8; g1.out_ld = I; g1.out_sf = hsf; g1.out_sf_ld = I / 32; g1.limit = m->swiglu_limit; g1.inter = I;
+        g1.N = 2 * I; g1.K = D; g1.x8 = w.x8s; g1.x8_rows = P + 128; g1.xsf = w.xsfs; g1.xsf_ld = D / 32;
+        g1.work = w.work; g1.n_work = w.n_work; g1.nd = nd; g1.rows_a = rows1; g1.dual = 1; g1.kb = 4; g1.epi = MX_EPI_SWIGLU_Q8;
+        g1.pair_w = w.pair_w; g1.out = w.hq8; g1.out_ld = I; g1.out_sf = w.hsf; g1.out_sf_ld = I / 32; g1.limit = m->swiglu_limit; g1.inter = I;
         if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
         if ((rc = mx_launch(g1, stream))) return rc;
         if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
         MxArgs g2{};
         g2.w = m->w2; g2.w_estride = (long long)D * (I / 2); g2.n_experts = shard_n; g2.a_fmt = MX_A_E2M1;
         g2.s = (const uint8_t*)m->s2; g2.s_estride = (long long)D * (I / 32); g2.s_rstride = I / 32; g2.s_row_shift = 0;
-        g2.N = D; g2.K = I; g2.x8 = hq8; g2.x8_rows = P; g2.xsf = hsf; g2.xsf_ld = I / 32;
-        g2.work = work; g2.n_work = n_work; g2.nd = MX_ND_DECODE; g2.rows_a = 64; g2.dual = 0; g2.kb = 4; g2.epi = MX_EPI_STORE_F32;
-        g2.pair_out = pair_out; g2.out = y2; g2.out_ld = D;
+        g2.N = D; g2.K = I; g2.x8 = w.hq8; g2.x8_rows = P + 128; g2.xsf = w.hsf; g2.xsf_ld = I / 32;
+        g2.work = w.work; g2.n_work = w.n_work; g2.nd = nd; g2.rows_a = rows2; g2.dual = 0; g2.kb = 4;
+        g2.epi = small ? MX_EPI_STORE_F32 : MX_EPI_ATOMIC_F32;
+        g2.pair_out = w.pair_out; g2.out = small ? w.y2 : w.acc; g2.out_ld = D;
         if ((rc = mx_launch(g2, stream))) return rc;
         if (shared) {
             MxArgs s1{};
             s1.w = m->sh_w13; s1.n_experts = 1; s1.a_fmt = MX_A_E4M3;
             s1.s = (const uint8_t*)m->sh_s13; s1.s_rstride = m->sh_s13_cols; s1.s_row_shift = 5;
-            s1.N = 2 * I; s1.K = D; s1.x8 = x8t; s1.x8_rows = T; s1.xsf = xsft; s1.xsf_ld = D / 32;
-            s1.work = nullptr; s1.dense_rows = T; s1.n_work_host = (T + MX_ND_DECODE - 1) / MX_ND_DECODE;
-            s1.nd = MX_ND_DECODE; s1.rows_a = 32; s1.dual = 1; s1.kb = 4; s1.epi = MX_EPI_SWIGLU_Q8;
-            s1.out = hs8; s1.out_ld = I; s1.out_sf = hssf; s1.out_sf_ld = I / 32; s1.limit = m->swiglu_limit; s1.inter = I; s1.round_gu_bf16 = 1;
+            s1.N = 2 * I; s1.K = D; s1.x8 = w.x8t; s1.x8_rows = T + 128; s1.xsf = w.xsft; s1.xsf_ld = D / 32;
+            s1.work = nullptr; s1.dense_rows = T; s1.n_work_host = (T + nd - 1) / nd;
+            s1.nd = nd; s1.rows_a = rows1; s1.dual = 1; s1.kb = 4; s1.epi = MX_EPI_SWIGLU_Q8;
+            s1.out = w.hs8; s1.out_ld = I; s1.out_sf = w.hssf; s1.out_sf_ld = I / 32; s1.limit = m->swiglu_limit; s1.inter = I; s1.round_gu_bf16 = 1;
             if ((rc = mx_launch(s1, stream))) return rc;
             MxArgs s2{};
             s2.w = m->sh_w2; s2.n_experts = 1; s2.a_fmt = MX_A_E4M3;
             s2.s = (const uint8_t*)m->sh_s2; s2.s_rstride = m->sh_s2_cols; s2.s_row_shift = 5;
-            s2.N = D; s2.K = I; s2.x8 = hs8; s2.x8_rows = T; s2.xsf = hssf; s2.xsf_ld = I / 32;
-            s2.work = nullptr; s2.dense_rows = T; s2.n_work_host = (T + MX_ND_DECODE - 1) / MX_ND_DECODE;
-            s2.nd = MX_ND_DECODE; s2.rows_a = 64; s2.dual = 0; s2.kb = 4; s2.epi = MX_EPI_STORE_BF16;
-            s2.out = ys; s2.out_ld = D;
+            s2.N = D; s2.K = I; s2.x8 = w.hs8; s2.x8_rows = T + 128; s2.xsf = w.hssf; s2.xsf_ld = I / 32;
+            s2.work = nullptr; s2.dense_rows = T; s2.n_work_host = (T + nd - 1) / nd;
+            s2.nd = nd; s2.rows_a = rows2; s2.dual = 0; s2.kb = 4; s2.epi = MX_EPI_STORE_BF16;
+            s2.out = w.ys; s2.out_ld = D;
             if ((rc = mx_launch(s2, stream))) return rc;
         }
-        const long n = (long)T * D;
-        moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y2, eid, shared ? ys : nullptr, (__nv_bfloat16*)m->out, m->routed_out, T, topk, D,
+    } else {
+        const __nv_bfloat16* xin = m->x_is_quantized ? (const __nv_bfloat16*)m->x : w.xq;
+        const int sbytes = m->expert_fmt == SK_FMT_FP4_BF16S ? 2 : 1;
+        // routed gate/up + SwiGLU * weight + fake quant -> hq [sorted pair, inter]
+        SkinnyArgs a{};
+        a.w = (const uint8_t*)m->w13; a.w_estride = (long long)2 * I * (D / 2); a.n_experts = shard_n;
+        a.s = (const uint8_t*)m->s13; a.s_estride = (long long)2 * I * (D / 32) * sbytes; a.s_rstride = (D / 32) * sbytes;
+        a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = D;
+        a.work = w.work; a.n_work = w.n_work; a.pair_tok = w.pair_tok; a.pair_out = nullptr; a.pair_w = w.pair_w;
+        a.out = w.hq; a.out_ld = I; a.limit = m->swiglu_limit; a.inter = I;
+        if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
+        if ((rc = skinny_launch(a, m->expert_fmt, SK_EPI_SWIGLU, stream))) return rc;
+        if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
+        // routed down -> y2 [original pair, dim] fp32
+        SkinnyArgs b{};
+        b.w = (const uint8_t*)m->w2; b.w_estride = (long long)D * (I / 2); b.n_experts = shard_n;
+        b.s = (const uint8_t*)m->s2; b.s_estride = (long long)D * (I / 32) * sbytes; b.s_rstride = (I / 32) * sbytes;
+        b.N = D; b.K = I; b.x = w.hq; b.x_ld = I;
+        b.work = w.work; b.n_work = w.n_work; b.pair_tok = nullptr; b.pair_out = w.pair_out; b.pair_w = nullptr;
+        b.out = w.y2; b.out_ld = D;
+        if ((rc = skinny_launch(b, m->expert_fmt, SK_EPI_STORE_F32, stream))) return rc;
+        if (shared) {
+            // shared expert: gu rounded to bf16, SwiGLU without weight, fake quant, down projection rounded to bf16 (dsv41/decode.py:461-463)
+            SkinnyArgs c{};
+            c.w = (const uint8_t*)m->sh_w13; c.s = (const uint8_t*)m->sh_s13;
+            c.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s13_cols : m->sh_s13_cols * 4;
+            c.N = 2 * I; c.K = D; c.x = xin; c.x_ld = D; c.w_permk = m->sh_permk;
+            c.work = nullptr; c.dense_rows = T; c.n_work_host = (T + SK_TOK - 1) / SK_TOK;
+            c.out = w.hs; c.out_ld = I; c.limit = m->swiglu_limit; c.inter = I; c.round_gu_bf16 = 1;
+            if ((rc = skinny_launch(c, m->shared_fmt, SK_EPI_SWIGLU, stream))) return rc;
+            SkinnyArgs d{};
+            d.w = (const uint8_t*)m->sh_w2; d.s = (const uint8_t*)m->sh_s2;
+            d.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s2_cols : m->sh_s2_cols * 4;
+            d.N = D; d.K = I; d.x = w.hs; d.x_ld = I; d.w_permk = m->sh_permk;
+            d.work = nullptr; d.dense_rows = T; d.n_work_host = (T + SK_TOK - 1) / SK_TOK;
+            d.out = w.ys; d.out_ld = D;
+            if ((rc = skinny_launch(d, m->shared_fmt, SK_EPI_STORE_BF16, stream))) return rc;
+        }
+    }
+    // ---- combine: routed sum (+ shared expert) -> bf16
+    const long n = (long)T * D;
+    if (small) {
+        moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.y2, w.eid, shared ? w.ys : nullptr, (__nv_bfloat16*)m->out, m->routed_out, T, topk, D,
                                                                            m->shard_start, shard_n);
         B200_CHECK_LAUNCH();
-        if (m->eid_out && (ce = cudaMemcpyAsync(m->eid_out, eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
-        if (m->wt_out && (ce = cudaMemcpyAsync(m->wt_out, wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
-        return 0;
+    } else {
+        if (m->out) {
+            moe_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.acc, shared ? w.ys : nullptr, (__nv_bfloat16*)m->out, n);
+            B200_CHECK_LAUNCH();
+        }
+        if (m->routed_out && (ce = cudaMemcpyAsync(m->routed_out, w.acc, sizeof(float) * n, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
     }
-    const __nv_bfloat16* xin = m->x_is_quantized ? (const __nv_bfloat16*)m->x : xq;
-    const int sbytes = m->expert_fmt == SK_FMT_FP4_BF16S ? 2 : 1;
-
-    // routed gate/up + SwiGLU * weight + fake quant -> hq [sorted pair, inter]
-    SkinnyArgs a{};
-    a.w = (const uint8_t*)m->w13; a.w_estride = (long long)2 * I * (D / 2); a.n_experts = shard_n;
-    a.s = (const uint8_t*)m->s13; a.s_estride = (long long)2 * I * (D / 32) * sbytes; a.s_rstride = (D / 32) * sbytes;
-    a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = D;
-    a.work = work; a.n_work = n_work; a.pair_tok = pair_tok; a.pair_out = nullptr; a.pair_w = pair_w;
-    a.out = hq; a.out_ld = I; a.limit = m->swiglu_limit; a.inter = I;
-    if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
-    int rc = skinny_launch(a, m->expert_fmt, SK_EPI_SWIGLU, stream);
-    if (rc) return rc;
-    if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
-    // routed down -> y2 [original pair, dim] fp32
-    SkinnyArgs b{};
-    b.w = (const uint8_t*)m->w2; b.w_estride = (long long)D * (I / 2); b.n_experts = shard_n;
-    b.s = (const uint8_t*)m->s2; b.s_estride = (long long)D * (I / 32) * sbytes; b.s_rstride = (I / 32) * sbytes;
-    b.N = D; b.K = I; b.x = hq; b.x_ld = I;
-    b.work = work; b.n_work = n_work; b.pair_tok = nullptr; b.pair_out = pair_out; b.pair_w = nullptr;
-    b.out = y2; b.out_ld = D;
-    rc = skinny_launch(b, m->expert_fmt, SK_EPI_STORE_F32, stream);
-    if (rc) return rc;
-    if (m->has_shared && m->out) {
-        // shared expert: gu rounded to bf16, SwiGLU without weight, fake quant, down projection rounded to bf16 (dsv41/decode.py:461-463)
-        SkinnyArgs c{};
-        c.w = (const uint8_t*)m->sh_w13; c.s = (const uint8_t*)m->sh_s13;
-        c.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s13_cols : m->sh_s13_cols * 4;
-        c.N = 2 * I; c.K = D; c.x = xin; c.x_ld = D; c.w_permk = m->sh_permk;
-        c.work = nullptr; c.dense_rows = T; c.n_work_host = (T + SK_TOK - 1) / SK_TOK;
-        c.out = hs; c.out_ld = I; c.limit = m->swiglu_limit; c.inter = I; c.round_gu_bf16 = 1;
-        rc = skinny_launch(c, m->shared_fmt, SK_EPI_SWIGLU, stream);
-        if (rc) return rc;
-        SkinnyArgs d{};
-        d.w = (const uint8_t*)m->sh_w2; d.s = (const uint8_t*)m->sh_s2;
-        d.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s2_cols : m->sh_s2_cols * 4;
-        d.N = D; d.K = I; d.x = hs; d.x_ld = I; d.w_permk = m->sh_permk;
-        d.work = nullptr; d.dense_rows = T; d.n_work_host = (T + SK_TOK - 1) / SK_TOK;
-        d.out = ys; d.out_ld = D;
-        rc = skinny_launch(d, m->shared_fmt, SK_EPI_STORE_BF16, stream);
-        if (rc) return rc;
-    }
-    const long n = (long)T * D;
-    moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y2, eid, (m->has_shared && m->out) ? ys : nullptr, (__nv_bfloat16*)m->out,
-                                                                       m->routed_out, T, topk, D, m->shard_start, shard_n);
-    B200_CHECK_LAUNCH();
-    if (m->eid_out) {
-        ce = cudaMemcpyAsync(m->eid_out, eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream);
-        if (ce != cudaSuccess) return (int)ce;
-    }
-    if (m->wt_out) {
-        ce = cudaMemcpyAsync(m->wt_out, wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream);
-        if (ce != cudaSuccess) return (int)ce;
-    }
+    if (m->eid_out && (ce = cudaMemcpyAsync(m->eid_out, w.eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
+    if (m->wt_out && (ce = cudaMemcpyAsync(m->wt_out, w.wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
     return 0;
 }
 

@@ -17,6 +17,7 @@
 // fp4_tcw.cu, expert_chain.cu for decode) when the activation is FP8-quantised, which it always is inside the MoE layer
 // (dsv41/model.py:2040, dsv41/fused.py:297-306).
 #include <cuda_fp8.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "mxgemm.cuh"
@@ -210,12 +211,13 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         for (int b = 0; b < nkb; ++b) {
                             // scale atoms of this k block -> TMEM: [A tile 0][A tile 1][B], 4 columns each
                             const uint32_t sfcol = tmem_base + MX_SF_COL0 + (s * KB + b) * (nt + 1) * 4;
-                            for (int q = 0; q <= nt; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * (nt + 1) + q) * 512u));
+                            if (!(a.dbg & 1) || n == 0) for (int q = 0; q <= nt; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * (nt + 1) + q) * 512u));
                             const uint64_t da0 = desc_sw128(sbase + (uint32_t)b * a_box);
                             const uint64_t da1 = desc_sw128(sbase + (uint32_t)(KB + b) * a_box);
                             const uint64_t db = desc_sw128(sbase + (uint32_t)(nt * KB) * a_box + (uint32_t)b * b_box);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {  // 4 MMAs of K = 32: operand descriptors advance by 32 bytes inside the swizzled row
+                                if ((a.dbg & 2) && j > 0) break;
                                 const uint32_t id = mx_idesc(a.a_fmt, nd, j);
                                 tc_mma_mx(d0, da0 + 2 * j, db + 2 * j, id, sfcol, sfcol + nt * 4, accumulate);
                                 if (nt == 2) tc_mma_mx(d0 + nd, da1 + 2 * j, db + 2 * j, id, sfcol + 4, sfcol + nt * 4, accumulate);
@@ -229,41 +231,73 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
             }
         } else if (warp >= 8) {
             // ------------------------------------------------ scale loaders: thread r = accumulator lane r = tile row r
+            // The loads of stage n + PD are in flight while stage n is stored (software pipeline over the flat stage sequence).
             const int r = tid - 256;
-            int wk = wk_lo, it = it_lo;
-            int4 w = get_work(wk);
-            uint32_t n = 0;
             const uint32_t atom_off = (uint32_t)(r & 31) * 16u + (uint32_t)(r >> 5) * 4u;
-            for (long item = lo; item < hi && !abort_flag; ++item) {
-                const int row0 = it * rows_item;
-                const bool arow = r < a.rows_a;
-                const uint8_t* sbase = a.s + (long long)w.x * a.s_estride;
+            const bool arow = r < a.rows_a;
+            struct Cur {
+                long item; int wk, it, st; int4 w;
+                const uint8_t *s_a, *s_b, *s_x; bool brow;
+            };
+            auto setup = [&](Cur& c) {
+                const int row0 = c.it * rows_item;
+                const uint8_t* sbase = a.s + (long long)c.w.x * a.s_estride;
                 const int ra = min(row0 + r, a.N - 1), rb = min(a.inter + row0 + r, a.N - 1);
-                const uint8_t* s_a = sbase + (long)(ra >> a.s_row_shift) * a.s_rstride;
-                const uint8_t* s_b = sbase + (long)(rb >> a.s_row_shift) * a.s_rstride;
-                const bool brow = r < w.z;
-                const uint8_t* s_x = a.xsf + (long)(w.y + (brow ? r : 0)) * a.xsf_ld;
-                for (int st = 0; st < spi; ++st, ++n) {
+                c.s_a = sbase + (long)(ra >> a.s_row_shift) * a.s_rstride;
+                c.s_b = sbase + (long)(rb >> a.s_row_shift) * a.s_rstride;
+                c.brow = r < c.w.z;
+                c.s_x = a.xsf + (long)(c.w.y + (c.brow ? r : 0)) * a.xsf_ld;
+            };
+            auto advance = [&](Cur& c) {
+                if (++c.st < spi) return;
+                c.st = 0;
+                ++c.item;
+                if (++c.it == ipw) { c.it = 0; ++c.wk; if (c.item < hi) c.w = get_work(c.wk); }
+                if (c.item < hi) setup(c);
+            };
+            constexpr int PD = 3;
+            uint32_t q[PD][3][4];
+            auto load = [&](const Cur& c, uint32_t (&v)[3][4]) {
+                if (c.item >= hi) return;
+                const int kb0 = c.st * KB, nkb = min(KB, kblocks - kb0);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (b >= nkb) break;
+                    const int g0 = (kb0 + b) * 4;  // first 32-k group of the k block
+                    v[0][b] = arow ? ldg_stream4(c.s_a + g0) : 0x7F7F7F7Fu;
+                    v[1][b] = (arow && nt == 2) ? ldg_stream4(c.s_b + g0) : 0x7F7F7F7Fu;
+                    v[2][b] = c.brow ? ldg_stream4(c.s_x + g0) : 0x7F7F7F7Fu;
+                }
+            };
+            Cur use;
+            use.item = lo; use.wk = wk_lo; use.it = it_lo; use.st = 0; use.w = get_work(wk_lo);
+            setup(use);
+            Cur ld = use;
+#pragma unroll
+            for (int i = 0; i < PD; ++i) { load(ld, q[i]); advance(ld); }
+            uint32_t n = 0;
+            while (use.item < hi && !abort_flag) {
+#pragma unroll
+                for (int i = 0; i < PD; ++i) {
+                    if (use.item >= hi) break;
                     const uint32_t s = n % NS, ph = (n / NS) & 1;
-                    const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
-                    uint32_t va[4], vb[4], vx[4];
-                    for (int b = 0; b < nkb && b < 4; ++b) {  // issue the loads before waiting for the slot
-                        const int g0 = (kb0 + b) * 4;         // first 32-k group of the k block
-                        va[b] = arow ? ldg_stream4(s_a + g0) : 0x7F7F7F7Fu;
-                        vb[b] = (arow && nt == 2) ? ldg_stream4(s_b + g0) : 0x7F7F7F7Fu;
-                        vx[b] = brow ? ldg_stream4(s_x + g0) : 0x7F7F7F7Fu;
-                    }
+                    const int kb0 = use.st * KB, nkb = min(KB, kblocks - kb0);
                     if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 31)) break;
                     uint8_t* sf = sf_ring + (size_t)s * sf_stage_bytes + atom_off;
-                    for (int b = 0; b < nkb && b < 4; ++b) {
-                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1)) * 512) = va[b];
-                        if (nt == 2) *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + 1) * 512) = vb[b];
-                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + nt) * 512) = vx[b];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        if (b >= nkb) break;
+                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1)) * 512) = q[i][0][b];
+                        if (nt == 2) *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + 1) * 512) = q[i][1][b];
+                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + nt) * 512) = q[i][2][b];
                     }
                     fence_async_smem();
                     mbar_arrive(bar_full_sf(s));
+                    advance(use);
+                    ++n;
+                    load(ld, q[i]);
+                    advance(ld);
                 }
-                if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
             }
         } else if (warp >= 4) {
             // ------------------------------------------------ epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31
@@ -315,6 +349,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                             const long orow = a.pair_out ? a.pair_out[prow] : prow;
                             if (row0 + r < a.N) {
                                 if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + row0 + r] = v;
+                                else if (a.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow * a.out_ld + row0 + r, v);
                                 else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + row0 + r] = __float2bfloat16_rn(v);
                             }
                         }
@@ -365,6 +400,7 @@ static int make_tmap(CUtensorMap* tm, CUtensorMapDataType dt, int rank, const vo
 
 int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     MxArgs a = a_in;
+    if (const char* e = getenv("B200_MX_DBG")) a.dbg = atoi(e);
     if (!a.w || !a.s || !a.x8 || !a.xsf || !a.out) return ERR_BAD_ARG;
     if (a.a_fmt != MX_A_E2M1 && a.a_fmt != MX_A_E4M3) return ERR_UNSUPPORTED;
     if (a.K <= 0 || a.K % 128 || a.N <= 0) return ERR_BAD_SHAPE;
@@ -377,15 +413,20 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
         return ERR_BAD_ALIGN;
     if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
     const int nt = a.dual ? 2 : 1;
+    // pipeline geometry: as many 128-wide k blocks per stage as still leave a ring of at least 3 stages
+    const size_t slack = 1024 + 16384;  // the A descriptors always span 128 rows: slack behind the ring for tiles that fetch fewer rows
     if (a.kb < 1 || a.kb > 4) a.kb = 4;
-    const size_t stage = (size_t)(nt * a.kb) * a.rows_a * 128 + (size_t)a.kb * a.nd * 128;
-    const size_t sf_stage = (size_t)a.kb * (nt + 1) * 512;
-    // the A descriptors always span 128 rows: keep 16 KB of slack behind the ring for tiles that fetch fewer rows
-    const size_t slack = 1024 + 16384;
-    int stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
-    if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
-    // scale columns in TMEM: stages * kb * (nt + 1) * 4 <= 256
-    while (stages > 1 && stages * a.kb * (nt + 1) * 4 > MX_TMEM_COLS - MX_SF_COL0) --stages;
+    int stages = 0;
+    size_t stage = 0, sf_stage = 0;
+    for (;; --a.kb) {
+        stage = (size_t)(nt * a.kb) * a.rows_a * 128 + (size_t)a.kb * a.nd * 128;
+        sf_stage = (size_t)a.kb * (nt + 1) * 512;
+        stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
+        if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
+        // scale columns in TMEM: stages * kb * (nt + 1) * 4 <= 256
+        while (stages > 1 && stages * a.kb * (nt + 1) * 4 > MX_TMEM_COLS - MX_SF_COL0) --stages;
+        if (stages >= 3 || a.kb == 1) break;
+    }
     if (stages < 2) return ERR_BAD_SHAPE;
     a.n_stages = stages;
     size_t smem = (size_t)stages * (stage + sf_stage) + slack;

@@ -12,7 +12,7 @@ constexpr int MX_SF_COL0 = 256;   // scale factors live in TMEM columns [256, 51
 constexpr int MX_MAX_STAGES = 8;
 constexpr int MX_SMEM_LIMIT = 227 * 1024 - 2048;
 
-enum { MX_EPI_STORE_F32 = 0, MX_EPI_SWIGLU_Q8 = 1, MX_EPI_STORE_BF16 = 2 };
+enum { MX_EPI_STORE_F32 = 0, MX_EPI_SWIGLU_Q8 = 1, MX_EPI_STORE_BF16 = 2, MX_EPI_ATOMIC_F32 = 3 };
 enum { MX_A_E4M3 = 0, MX_A_E2M1 = 5 };  // operand format codes of the tensor-core instruction descriptor
 
 struct MxArgs {
@@ -51,6 +51,7 @@ struct MxArgs {
     float limit;
     int inter;
     int round_gu_bf16;
+    int dbg;                // timing experiments only
 };
 
 int mx_launch(const MxArgs& a, cudaStream_t stream);

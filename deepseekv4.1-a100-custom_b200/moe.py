@@ -35,17 +35,20 @@ class MoELayer:
         self.topk, self.gate_bias, self.gate_temp, self.route_scale = topk, gate_bias, gate_temp, route_scale
         self.score_func, self.norm, self.swiglu_limit = score_func, norm_topk_prob and topk > 1, swiglu_limit
         self.device = dev
-        # engine 0 = automatic, 1 = weight streaming with in-register dequantisation, 2 = block-scaled tensor cores.  The tensor-core
-        # path reads the shared expert in natural k order, so a natural-order copy is kept next to the W8 container.
+        # engine 0 = automatic (weight streaming up to 64 tokens, block-scaled tensor cores beyond), 1 = weight streaming with
+        # in-register dequantisation, 2 = block-scaled tensor cores.  The tensor-core path reads the shared expert in natural k
+        # order, so a natural-order copy is kept next to the W8 container.
         self.engine = engine
         self._mx_ok = (self.expert_fmt == L.FMT_FP4_E8M0 and (sh_w13 is None or sh_w13.s8.dtype == torch.uint8) and self.dim % 128 == 0 and self.inter % 128 == 0)
         if engine == 2 and not self._mx_ok:
             raise ValueError("engine 2 needs E8M0 scales for the experts and the shared expert and dims that are multiples of 128")
-        self._use_mx = engine == 2 or (engine == 0 and self._mx_ok)
         self._sh_nat = None
-        if self._use_mx and sh_w13 is not None:
+        if self._mx_ok and engine != 1 and sh_w13 is not None:
             from .w8 import unpermute_k
             self._sh_nat = (unpermute_k(sh_w13.w8), unpermute_k(sh_w2.w8))
+
+    def _use_mx(self, tokens: int) -> bool:
+        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 64)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, *, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
                 x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, prof_events=None):
@@ -57,6 +60,7 @@ class MoELayer:
         T = x.shape[0]
         assert logits.shape == (T, self.n_experts) and logits.dtype in (torch.float32, torch.bfloat16) and logits.is_contiguous()
         lib = L.lib()
+        mx = self._use_mx(T)
         if final and out is None:
             out = torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16)
         routed = torch.empty(T, self.dim, device=dev, dtype=torch.float32) if want_routed else None
@@ -76,17 +80,17 @@ class MoELayer:
         shared = with_shared and self.sh_w13 is not None and final
         a.has_shared = int(shared)
         if shared:
-            w13b, w2b = (self._sh_nat if self._use_mx else (self.sh_w13.w8, self.sh_w2.w8))
+            w13b, w2b = (self._sh_nat if mx else (self.sh_w13.w8, self.sh_w2.w8))
             a.sh_w13, a.sh_s13, a.sh_w2, a.sh_s2 = w13b.data_ptr(), self.sh_w13.s8.data_ptr(), w2b.data_ptr(), self.sh_w2.s8.data_ptr()
             a.shared_fmt = L.FMT_FP8_E8M0 if self.sh_w13.s8.dtype == torch.uint8 else L.FMT_FP8_F32B
-            a.sh_s13_cols, a.sh_s2_cols, a.sh_permk = self.sh_w13.s8.shape[1], self.sh_w2.s8.shape[1], int(not self._use_mx)
+            a.sh_s13_cols, a.sh_s2_cols, a.sh_permk = self.sh_w13.s8.shape[1], self.sh_w2.s8.shape[1], int(not mx)
         a.swiglu_limit = float(self.swiglu_limit)
         a.out = out.data_ptr() if final else None
         a.routed_out = routed.data_ptr() if routed is not None else None
         a.eid_out = eid.data_ptr() if eid is not None else None
         a.wt_out = wt.data_ptr() if wt is not None else None
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        a.engine = 2 if self._use_mx else 1
+        a.engine = 2 if mx else 1
         if prof_events is not None:  # (start, stop) torch.cuda.Event pair, already created (recorded once), timing enabled
             a.prof_start, a.prof_stop = prof_events[0].cuda_event, prof_events[1].cuda_event
         with torch.cuda.device(dev):

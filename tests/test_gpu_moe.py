@@ -90,3 +90,23 @@ def test_shard_partials_sum_to_full_layer(mods, oracle, dev):
         assert rel_err(r, ref["routed"]) <= 1e-2
         acc += r
     assert rel_err(acc, routed_full) < 1e-5
+
+
+@pytest.mark.parametrize("T", [100, 300, 800])
+def test_layer_prefill_sized_batches(mods, oracle, dev, T):
+    """More than 64 tokens run on the block-scaled tensor cores; more than 4096 pairs use the multi-block bucketing and the
+    per-token accumulator (T = 800, top-6)."""
+    topk = 4 if T < 800 else 6
+    _check(mods, oracle, dev, E=16, D=512, I=256, topk=topk, T=T, seed=900 + T, lo=116, hi=122)
+    assert mods.cukern.device_error(dev) == 0
+
+
+def test_layer_prefill_shard(mods, oracle, dev):
+    T, E, D, I, topk = 900, 16, 512, 256, 6
+    ex, sh, part = _layer(mods, dev, E, D, I, topk, 31, lo=116, hi=122, shard=(4, 8))
+    x = mods.synth.make_tokens(T, D, 32)
+    logits = mods.synth.make_logits(T, E, 33, topk=topk)
+    r = part.forward(x.to(dev), logits.to(dev), final=False, want_routed=True)
+    ref = oracle.moe_layer(x, logits.float(), None, ex["w13"][4:12], ex["s13"][4:12], ex["w2"][4:12], ex["s2"][4:12], None, topk=topk, shard=(4, 8), n_experts=E)
+    assert rel_err(r, ref["routed"]) <= 1e-2
+    assert mods.cukern.device_error(dev) == 0
