@@ -30,7 +30,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 E, D, I, TOPK = 384, 4096, 2048, 6
-WORKLOADS = {"decode64": 64, "decode32": 32, "decode8": 8, "decode1": 1}
+WORKLOADS = {"decode64": 64, "decode32": 32, "decode8": 8, "decode1": 1, "prefill4096": 4096}
 POOL = 12             # distinct (tokens, logits) sets cycled over the steps
 ROTATE = 29           # expert-id shift of the Zipf ranking between consecutive sets: hot experts change every step
 SEED = 1234
@@ -46,6 +46,16 @@ def measured_peaks():
         except Exception:
             pass
     return 6650.0, "fallback (6.65 TB/s)"
+
+
+def measured_tensor_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["bf16_tflops"]), "measured bf16 burst (MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return 1590.0, "fallback (1.59 PFLOP/s bf16)"
 
 
 class ClockSampler:
@@ -179,16 +189,21 @@ def run_reference(args):
 
 def workload_config(name: str, gpus: int) -> dict:
     S = WORKLOADS[name]
-    return {"workload": f"moe_{name}: {S} decode tokens, 384 experts (FP4 e2m1 + E8M0/32), hidden 4096, inter 2048, top-6 Zipf(s=1) softmax routing, "
+    kind = "decode" if S <= 64 else "prefill"
+    return {"workload": f"moe_{name}: {S} {kind} tokens, 384 experts (FP4 e2m1 + E8M0/32), hidden 4096, inter 2048, top-6 Zipf(s=1) softmax routing, "
                         f"+1 FP8 (e4m3 + E8M0 32x32) shared expert", "tokens": S, "experts": E, "hidden": D, "inter": I, "topk": TOPK,
             "parallelism": "single GPU, all experts resident" if gpus == 1 else f"ep{gpus}: experts sharded {E // gpus}/GPU, tokens split {S}/{gpus}",
-            "l2": f"inputs larger than L2: {POOL} token/logit sets cycle, Zipf ranking rotated by {ROTATE} experts per set over 5.13 GB of experts"}
+            "l2": f"inputs larger than L2: {pool_size(S)} token/logit sets cycle, Zipf ranking rotated by {ROTATE} experts per set over 5.13 GB of experts"}
 
 
 # ----------------------------------------------------------------------------------------------------------------- GPU arm
+def pool_size(S: int) -> int:
+    return POOL if S <= 64 else 3
+
+
 def build_inputs(synth, S: int, dev):
     xs, ls = [], []
-    for i in range(POOL):
+    for i in range(pool_size(S)):
         xs.append(synth.make_tokens(S, D, SEED + 10 + i))
         ls.append(synth.make_logits(S, E, SEED + 3, topk=TOPK, rotate=ROTATE * i))
     return xs, ls
@@ -252,8 +267,9 @@ def run_gpu(args):
     epl = ep.EPMoE(layer) if world > 1 else None
 
     # unique experts touched per input set (bookkeeping for the byte counts; untimed)
+    NP = pool_size(S)
     uniq = []
-    for i in range(POOL):
+    for i in range(NP):
         _, eid, _ = layer.forward(xs_h[i].to(dev), ls_h[i].to(dev), want_route=True)
         uniq.append(int(torch.unique(eid).numel()))
     torch.cuda.synchronize()
@@ -266,7 +282,7 @@ def run_gpu(args):
     torch.cuda.synchronize()
 
     def step_resident(i):
-        j = i % POOL
+        j = i % NP
         if world == 1:
             layer.forward(xs[j], ls[j], out=out, prof_events=prof[i])
         else:
@@ -286,7 +302,7 @@ def run_gpu(args):
     xd, ld = torch.empty_like(xs[0]), torch.empty_like(ls[0])
 
     def step_e2e(i):
-        j = i % POOL
+        j = i % NP
         xd.copy_(xh[j], non_blocking=True)
         ld.copy_(lh[j], non_blocking=True)
         if world == 1:
@@ -310,20 +326,33 @@ def run_gpu(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.workload, world), "clocks": clocks,
             "e2e": {"value": S / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
-            "gpu_launches": (6 if world == 1 else 9) * args.steps}
+            "gpu_launches": ((6 if S <= 64 else 11) if world == 1 else (9 if S <= 64 else 14)) * args.steps}
     if world == 1:
         durs = [prof[args.warmup + i][0].elapsed_time(prof[args.warmup + i][1]) for i in range(args.steps)]
-        u_steps = [uniq[(args.warmup + i) % POOL] for i in range(args.steps)]
-        alg = statistics.mean(u_steps) * exp_b13
+        u_steps = [uniq[(args.warmup + i) % NP] for i in range(args.steps)]
         avg_ms = statistics.mean(durs)
-        achieved = alg / (avg_ms * 1e-3) / 1e9
         layer_bytes = statistics.mean(u_steps) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
-        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                            "kernel": "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)",
-                            "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
-                            "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": statistics.mean(u_steps),
-                            "whole_layer": {"bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
-                                            "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak}}
+        if S <= 64:
+            alg = statistics.mean(u_steps) * exp_b13
+            achieved = alg / (avg_ms * 1e-3) / 1e9
+            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                                "kernel": "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)",
+                                "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
+                                "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": statistics.mean(u_steps),
+                                "whole_layer": {"bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
+                                                "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak}}
+        else:
+            tpeak, tsrc = measured_tensor_peak()
+            flops1 = S * TOPK * 2.0 * D * 2 * I          # routed gate/up grouped GEMM (the timed kernel)
+            flops_layer = S * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)
+            achieved = flops1 / (avg_ms * 1e-3) / 1e12
+            line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak, "traffic": None,
+                                "kernel": "mx_gemm_kernel (routed gate/up grouped GEMM, tcgen05 kind::mxf8f6f4 block-scaled, + SwiGLU + FP8 quant)",
+                                "algorithmic_flops_per_launch": flops1, "avg_launch_ms": avg_ms, "peak_source": tsrc,
+                                "unique_experts_per_step": statistics.mean(u_steps),
+                                "whole_layer": {"routed_flops_per_step": flops_layer, "achieved_tflops": flops_layer / (ms * 1e-3) / 1e12,
+                                                "frac": flops_layer / (ms * 1e-3) / 1e12 / tpeak, "weight_bytes_per_step": layer_bytes,
+                                                "weight_stream_floor_ms": layer_bytes / (peak * 1e9) * 1e3}}
         # other decode batch sizes of the same configuration (short runs, same method)
         sweep = {}
         if not args.no_sweep:
@@ -333,14 +362,21 @@ def run_gpu(args):
                 xs2, ls2 = build_inputs(synth, s2, dev)
                 xs2, ls2 = [x.to(dev) for x in xs2], [l.to(dev) for l in ls2]
                 o2 = torch.empty(s2, D, device=dev, dtype=torch.bfloat16)
+                np2 = pool_size(s2)
                 u2 = []
-                for i in range(POOL):
+                for i in range(np2):
                     _, eid, _ = layer.forward(xs2[i], ls2[i], want_route=True)
                     u2.append(int(torch.unique(eid).numel()))
-                m2 = time_steps(lambda i: layer.forward(xs2[i % POOL], ls2[i % POOL], out=o2), args.steps, args.warmup, barrier)
+                k2 = args.steps if s2 <= 64 else max(3, min(args.steps, 8))
+                m2 = time_steps(lambda i: layer.forward(xs2[i % np2], ls2[i % np2], out=o2), k2, args.warmup, barrier)
                 b2 = statistics.mean(u2) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
                 sweep[name] = {"tokens_per_s": s2 / (m2 * 1e-3), "ms_per_step": m2, "unique_experts": statistics.mean(u2), "layer_gbs": b2 / (m2 * 1e-3) / 1e9,
                                "layer_hbm_frac": b2 / (m2 * 1e-3) / 1e9 / peak}
+                if s2 > 64:
+                    f2 = s2 * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)
+                    sweep[name]["routed_tflops"] = f2 / (m2 * 1e-3) / 1e12
+                    sweep[name]["frac_of_bf16_peak"] = f2 / (m2 * 1e-3) / 1e12 / measured_tensor_peak()[0]
+                del xs2, ls2, o2
         line["sweep"] = sweep
         if not args.no_cpu:
             tps, dt, done, desc = time_cpu_chain(S, 10 ** 9, 1, budget_s=args.cpu_seconds)
