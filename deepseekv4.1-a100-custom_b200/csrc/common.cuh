@@ -77,7 +77,11 @@ __device__ __forceinline__ float swiglu_bf16(float g, float u, float wt, float l
         u = fminf(fmaxf(u, -limit), limit);
         g = fminf(g, limit);
     }
-    float v = wt * __fdiv_rn(g, 1.f + expf(-g)) * u;
+    // g / (1 + e^-g) with an IEEE division, as the reference computes it.  Below g = -80 the denominator leaves the range the
+    // hardware divides without its (very slow) denormal path; there silu(g) = g * e^g to within one ulp of a value < 1e-32.
+    float sl = __fdiv_rn(g, 1.f + expf(-fmaxf(g, -80.f)));
+    if (g < -80.f) sl = g * expf(g);
+    float v = wt * sl * u;
     return round_bf16(v);
 }
 

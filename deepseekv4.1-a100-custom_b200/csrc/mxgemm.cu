@@ -321,36 +321,54 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         if (nt == 2) tc_ld16(t0 + nd + c0, u);
                         tc_wait_ld();
                     }
-                    if (!active) continue;
+                    if (!active || (a.dbg & 4)) continue;
+                    // per-column metadata of the chunk, fetched with independent loads before the math
+                    float pw[16];
+                    long orow[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int prow = w.y + min(c0 + c, w.z - 1);
+                        pw[c] = a.pair_w ? __ldg(a.pair_w + prow) : 1.f;
+                        orow[c] = a.pair_out ? (long)__ldg(a.pair_out + prow) : (long)prow;
+                    }
                     if (a.epi == MX_EPI_SWIGLU_Q8) {
-                        // lane = SwiGLU column row0 + r; the 32 lanes of the warp are one quantisation group (dsv41/fused.py:285-306)
+                        // lane = SwiGLU column row0 + r; the 32 lanes of the warp are one quantisation group (dsv41/fused.py:285-306).
+                        // The 16 token columns of the chunk are processed as 16 independent chains (columns past the work's last
+                        // token compute on garbage and are not stored).
+                        const bool in_range = row0 + r < a.inter;
+                        float h[16], am[16];
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
-                            if (c0 + c >= w.z) break;
                             float gt = __uint_as_float(g[c]), up = __uint_as_float(u[c]);
                             if (a.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
-                            const int prow = w.y + c0 + c;
-                            const float h = swiglu_bf16(gt, up, a.pair_w ? a.pair_w[prow] : 1.f, a.limit);
-                            const float sc = fp8_group_scale(warp_max(fabsf(h)));
-                            const float qv = fminf(fmaxf(__fdiv_rn(h, sc), -448.f), 448.f);
-                            const long orow = a.pair_out ? a.pair_out[prow] : prow;
-                            if (row0 + r < a.inter) {
-                                reinterpret_cast<uint8_t*>(a.out)[orow * a.out_ld + row0 + r] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
-                                if (lane == 0) a.out_sf[orow * a.out_sf_ld + ((row0 + r) >> 5)] = (uint8_t)((f32_as_u32(sc) >> 23) & 0xFFu);
+                            h[c] = swiglu_bf16(gt, up, pw[c], a.limit);
+                            am[c] = fabsf(h[c]);
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) am[c] = fmaxf(am[c], __shfl_xor_sync(0xffffffffu, am[c], o));
+                        }
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const float sc = fp8_group_scale(am[c]);
+                            const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
+                            const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact (sc is a power of two)
+                            const float qv = fminf(fmaxf(h[c] * inv, -448.f), 448.f);
+                            if (in_range && c0 + c < w.z) {
+                                reinterpret_cast<uint8_t*>(a.out)[orow[c] * a.out_ld + row0 + r] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
+                                if (lane == 0) a.out_sf[orow[c] * a.out_sf_ld + ((row0 + r) >> 5)] = (uint8_t)sb;
                             }
                         }
                     } else {
+                        const bool in_range = row0 + r < a.N;
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
-                            if (c0 + c >= w.z) break;
-                            const int prow = w.y + c0 + c;
-                            float v = __uint_as_float(g[c]);
-                            if (a.pair_w) v *= a.pair_w[prow];
-                            const long orow = a.pair_out ? a.pair_out[prow] : prow;
-                            if (row0 + r < a.N) {
-                                if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + row0 + r] = v;
-                                else if (a.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow * a.out_ld + row0 + r, v);
-                                else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + row0 + r] = __float2bfloat16_rn(v);
+                            const float v = __uint_as_float(g[c]) * pw[c];
+                            if (in_range && c0 + c < w.z) {
+                                if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow[c] * a.out_ld + row0 + r] = v;
+                                else if (a.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow[c] * a.out_ld + row0 + r, v);
+                                else reinterpret_cast<__nv_bfloat16*>(a.out)[orow[c] * a.out_ld + row0 + r] = __float2bfloat16_rn(v);
                             }
                         }
                     }
