@@ -63,6 +63,16 @@ __device__ __forceinline__ float fp8_group_scale(float amax) {
     return pow2_ceil(__fdiv_rn(amax, 448.f));
 }
 
+// Same scale without the division, valid when amax carries at most 8 significant bits (a bf16 value, or the 1e-4 floor):
+// amax = M * 2^E, 448 = 1.75 * 2^8, so ceil(log2(amax / 448)) = E - 8 + (M > 1.75); amax / 448 can only be a power of two
+// when M == 1.75 exactly.
+__device__ __forceinline__ float fp8_group_scale_bf16(float amax) {
+    amax = fmaxf(amax, 1e-4f);
+    const uint32_t b = f32_as_u32(amax);
+    const uint32_t e = ((b >> 23) & 0xFF) - 8 + ((b & 0x7FFFFF) > 0x600000 ? 1 : 0);
+    return u32_as_f32(e << 23);
+}
+
 // quantise-dequantise one value with a power-of-two scale s (division by s is exact)
 __device__ __forceinline__ float fp8_fake_quant_value(float v, float s) {
     float q = __fdiv_rn(v, s);

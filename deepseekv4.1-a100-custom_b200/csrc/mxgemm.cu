@@ -9,7 +9,7 @@
 // Warp roles of the persistent CTA:
 //   warp 0      TMA producer: boxes of the weight tile(s) and of the activation rows into a shared-memory ring
 //   warp 1      allocates TMEM; one thread copies the scale atoms into TMEM (tcgen05.cp) and issues the MMAs
-//   warps 4-7   epilogue: tcgen05.ld of the accumulator lanes of their TMEM sub-partition, SwiGLU + FP8 quantisation or store
+//   warps 4-7, 12-15  epilogue: tcgen05.ld of the accumulator lanes of their TMEM sub-partition, SwiGLU + FP8 quantisation or store
 //   warps 8-11  scale loaders: one thread per tile row builds the 32x4x4 scale atoms in shared memory
 // Every wait is bounded; a wait that runs out of time records a code in a device error word and the CTA runs to its end.
 //
@@ -133,7 +133,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full(b), 1);
-            mbar_init(bar_acc_empty(b), 128);
+            mbar_init(bar_acc_empty(b), 256);
         }
         mbar_fence_init();
     }
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                     tc_commit(bar_acc_full(buf));
                 }
             }
-        } else if (warp >= 8) {
+        } else if (warp >= 8 && warp < 12) {
             // ------------------------------------------------ scale loaders: thread r = accumulator lane r = tile row r
             // The loads of stage n + PD are in flight while stage n is stored (software pipeline over the flat stage sequence).
             const int r = tid - 256;
@@ -300,8 +300,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 }
             }
         } else if (warp >= 4) {
-            // ------------------------------------------------ epilogue: warp q reads TMEM lanes 32 q .. 32 q + 31
-            const int q = warp - 4;
+            // ------------------------------------------------ epilogue: warps 4-7 and 12-15; warp q (mod 4) reads TMEM lanes
+            // 32 q .. 32 q + 31, the first group takes the even 16-column chunks, the second the odd ones
+            const int q = warp & 3, egrp = warp >= 12 ? 1 : 0;
             const int r = q * 32 + lane;  // tile row
             int wk = wk_lo, it = it_lo;
             int4 w = get_work(wk);
@@ -313,7 +314,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 const int row0 = it * rows_item;
                 const bool active = (q * 32 < a.rows_a) && ready;  // warp-uniform
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
-                for (int c0 = 0; c0 < nd; c0 += 16) {
+                for (int c0 = egrp * 16; c0 < nd; c0 += 32) {
                     if (c0 >= w.z) break;  // no tokens in these columns
                     uint32_t g[16], u[16];
                     if (active) {
@@ -351,7 +352,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         }
 #pragma unroll
                         for (int c = 0; c < 16; ++c) {
-                            const float sc = fp8_group_scale(am[c]);
+                            const float sc = fp8_group_scale_bf16(am[c]);  // am is a bf16 value
                             const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
                             const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact (sc is a power of two)
                             const float qv = fminf(fmaxf(h[c] * inv, -448.f), 448.f);

@@ -6,7 +6,7 @@
 
 namespace b200 {
 
-constexpr int MX_THREADS = 384;   // 12 warps: TMA producer, MMA issuer, 2 spare, 4 epilogue, 4 scale loaders
+constexpr int MX_THREADS = 512;   // 16 warps: TMA producer, MMA issuer, 2 spare, 4 epilogue, 4 scale loaders, 4 more epilogue
 constexpr int MX_TMEM_COLS = 512;
 constexpr int MX_SF_COL0 = 256;   // scale factors live in TMEM columns [256, 512)
 constexpr int MX_MAX_STAGES = 8;
