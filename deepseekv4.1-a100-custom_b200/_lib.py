@@ -45,6 +45,8 @@ _SIGNATURES = {
     "b200_fp4_grouped_workspace_bytes": (c_sz, [c_i]),
     "b200_fp4_grouped_gemm": (c_i, [c_p, c_ll, c_i, c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i,
                                     c_p, c_ll, c_p, c_sz, c_p]),
+    "b200_fp4_grouped_gemm_static": (c_i, [c_p, c_ll, c_i, c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_i, c_i, c_i,
+                                           c_i, c_i, c_p, c_ll, c_p]),
     "b200_fp8_gemm": (c_i, [c_p, c_ll, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_ll, c_p]),
     "b200_moe_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "b200_moe_forward": (c_i, [ctypes.POINTER(MoeArgs), c_p]),

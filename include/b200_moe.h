@@ -100,6 +100,21 @@ int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void
                           const float* pair_w, int n_pairs, int shard_start, int shard_n, int zero_out, int accumulate, float* out, long long out_ld,
                           void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+/* ---- the same grouped FP4 expert GEMM with its scratch inside the library: no workspace argument, and the call obtains no
+ * memory from the CUDA runtime or anyone else.  No counterpart in the reference.  Arguments, kernels and results are those of
+ * b200_fp4_grouped_gemm.  The work list lives in one fixed array per device (about 64 KB, part of the library's device
+ * image), so n_pairs is limited to B200_STATIC_MAX_PAIRS; more returns B200_ERR_TOO_LARGE and launches nothing.
+ *   - set-up: the first call on each device looks the array's address up (cudaGetSymbolAddress, result cached); make that
+ *     call before any stream capture begins;
+ *   - every call on a device shares the array.  Nothing in it has to start at zero or be cleared between calls: each call
+ *     rewrites all it reads.  Calls on one stream are ordered and safe; calls that can overlap on the device (other
+ *     streams) race on it and must be serialised by the caller, or use the workspace form above. */
+#define B200_STATIC_MAX_PAIRS 4096
+int b200_fp4_grouped_gemm_static(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s, long long s_estride,
+                                 int fmt, int n_local_experts, int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count,
+                                 int n_groups, const int* pair_tok, const int* pair_out, const float* pair_w, int n_pairs, int shard_start, int shard_n,
+                                 int zero_out, int accumulate, float* out, long long out_ld, cudaStream_t stream);
+
 /* ---- block-scaled FP8 dense GEMV / small-M GEMM.  Replaces fp8_gemv (dsv41/cukern.py:80-96), fp8_gemv_m1
  * (dsv41/cukern.py:116-133) and fp8_gemm_tc (dsv41/cukern.py:165-221, group_cols = 0).
  *   out[m, :] = x[m, :] @ dequant(w8, s)^T;  x bf16 [M, K] (row stride x_ld); w8 e4m3 [N, K];
