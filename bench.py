@@ -256,7 +256,7 @@ def run_gpu(args):
         torch.cuda.empty_cache()
     sh = synth.make_shared(D, I, seed=SEED + 1, kind="e8m0", device=dev)
     layer = moe.MoELayer(ex["w13"], ex["s13"], ex["w2"], ex["s2"], n_experts=E, topk=TOPK, sh_w13=w8.W8(sh["w13"], sh["s13"]), sh_w2=w8.W8(sh["w2"], sh["s2"]),
-                         swiglu_limit=10.0, shard_start=start)
+                         swiglu_limit=10.0, shard_start=start, engine=args.engine)
     xs_h, ls_h = build_inputs(synth, S, dev)
     counts = [c for _, c in ep.split_tokens(S, world)]
     first = sum(counts[:rank])
@@ -336,7 +336,8 @@ def run_gpu(args):
             alg = statistics.mean(u_steps) * exp_b13
             achieved = alg / (avg_ms * 1e-3) / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                                "kernel": "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)",
+                                "kernel": ("mx_gemm_kernel (routed gate/up weight stream on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)" if layer._use_mx(S)
+                                           else "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"),
                                 "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
                                 "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": statistics.mean(u_steps),
                                 "whole_layer": {"bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
@@ -396,7 +397,10 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--engine", type=int, default=0, choices=[0, 1, 2], help="0 automatic, 1 weight-streaming kernels, 2 tcgen05 block-scaled kernels")
+    ap.add_argument("--experts", type=int, default=E, help="expert count (smaller than the workload's 384 only for profiler captures)")
     args = ap.parse_args()
+    globals()["E"] = args.experts
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

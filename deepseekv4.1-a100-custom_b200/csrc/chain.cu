@@ -13,7 +13,7 @@ namespace b200 {
 constexpr int ROUTE_THREADS = 128;
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
-constexpr int MX_ND_DECODE = 16;        // token columns per work of the block-scaled tensor-core path
+constexpr int MX_ND_DECODE = 32;        // tokens per work of the block-scaled tensor-core path
 
 struct RouteArgs {
     int tokens, E, topk, dim;
@@ -436,7 +436,9 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         // activations -> e4m3 + E8M0 (the FP8 fake quantisation kept in quantised form), gathered into pair-sorted order
         if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream))) return rc;
         if (shared && (rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, nullptr, T, D, w.x8t, w.xsft, stream))) return rc;
-        const int rows1 = small ? 32 : 128, rows2 = small ? 64 : 128;
+        // weight rows per tile: as many as the tensor-core instruction takes (256) once there are enough (work, tile) items to
+        // balance over the SMs; fewer rows per tile for the smallest batches
+        const int rows1 = P >= 48 ? 128 : (P >= 24 ? 64 : 32), rows2 = 2 * rows1;
         MxArgs g1{};
         g1.w = m->w13; g1.w_estride = (long long)2 * I * (D / 2); g1.n_experts = shard_n; g1.a_fmt = MX_A_E2M1;
         g1.s = (const uint8_t*)m->s13; g1.s_estride = (long long)2 * I * (D / 32); g1.s_rstride = D / 32; g1.s_row_shift = 0;

@@ -71,10 +71,10 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
 __device__ __forceinline__ uint64_t desc_sf_atom(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
 }
-// instruction descriptor of kind::mxf8f6f4.block_scale: A format, B = e4m3, both K-major, N, E8M0 scales, M = 128,
-// scale byte j of the 4 in a TMEM column for both operands
-__device__ __forceinline__ uint32_t mx_idesc(int a_fmt, int nd, int j) {
-    return ((uint32_t)j << 4) | ((uint32_t)a_fmt << 7) | (0u << 10) | ((uint32_t)(nd >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24) |
+// instruction descriptor of kind::mxf8f6f4.block_scale: A = e4m3 (the tokens), B format (the weights), both K-major, N, E8M0
+// scales, M = 128, scale byte j of the 4 in a TMEM column for both operands
+__device__ __forceinline__ uint32_t mx_idesc(int b_fmt, int n, int j) {
+    return ((uint32_t)j << 4) | (0u << 7) | ((uint32_t)b_fmt << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24) |
            ((uint32_t)j << 29);
 }
 
@@ -84,29 +84,31 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
                  : "memory");
 }
 
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
-
 // ------------------------------------------------------------------ the kernel
-struct MxSmem {  // offsets inside the 1024-byte aligned dynamic window
-    uint32_t a_tile, b_tile, sf_atom, stage, a_off, b_off, sf_off;
-};
-
-__global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, const __grid_constant__ CUtensorMap tm_a,
-                                                                 const __grid_constant__ CUtensorMap tm_b) {
+// Tile orientation: the tokens of a work are the M side of the tensor-core tile (128 accumulator lanes, of which the first
+// `ntok` carry data), the weight rows are the N side (up to 256 per MMA: the MMA time hardly depends on N, so every
+// instruction should carry as many weight bytes as possible).  D[token, weight row] lives in TMEM columns [0, N_w).
+//   dual (SwiGLU epilogue): N_w = 2 * rows_w, columns [0, rows_w) = gate rows row0.., columns [rows_w, 2 rows_w) = up rows
+//   single:                 N_w = rows_w consecutive rows
+__global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, const __grid_constant__ CUtensorMap tm_w,
+                                                                 const __grid_constant__ CUtensorMap tm_x) {
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long bars[3 * MX_MAX_STAGES + 4];  // full_ab[s], full_sf[s], empty[s], acc_full[2], acc_empty[2]
     __shared__ uint32_t tmem_base_sh;
     __shared__ int abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int NS = a.n_stages, KB = a.kb, nd = a.nd, nt = a.dual ? 2 : 1;
+    const int NS = a.n_stages, KB = a.kb, nd = a.nd, rows_w = a.rows_a;
+    const int NW = a.dual ? 2 * rows_w : rows_w;   // N of the MMA
+    const int n_sfb = (NW + 127) >> 7;             // scale atoms of the weight side
+    const int n_atoms = 1 + n_sfb;
     uint8_t* base = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-    // stage layout: [tile][kb] A boxes (rows_a x 128 B each), then [kb] B boxes (nd x 128 B)
-    const uint32_t a_box = (uint32_t)a.rows_a * 128u, b_box = (uint32_t)nd * 128u;
-    const uint32_t stage_bytes = (uint32_t)(nt * KB) * a_box + (uint32_t)KB * b_box;  // multiple of 1024 (rows_a, nd multiples of 8)
+    // stage layout: [kb] token boxes (nd x 128 B), then [kb] weight tiles (NW x 128 B; dual: gate box then up box)
+    const uint32_t x_box = (uint32_t)nd * 128u, w_half = (uint32_t)rows_w * 128u, w_tile = (uint32_t)NW * 128u;
+    const uint32_t stage_bytes = (uint32_t)KB * (x_box + w_tile);
     uint8_t* ring = base;
-    uint8_t* sf_ring = base + (size_t)NS * stage_bytes;   // per stage: [kb][nt + 1] atoms of 512 B
-    const uint32_t sf_stage_bytes = (uint32_t)KB * (nt + 1) * 512u;
+    uint8_t* sf_ring = base + (size_t)NS * stage_bytes;   // per stage: [kb][n_atoms] atoms of 512 B
+    const uint32_t sf_stage_bytes = (uint32_t)(KB * n_atoms) * 512u;
     auto bar_full_ab = [&](int s) { return smem_u32(&bars[s]); };
     auto bar_full_sf = [&](int s) { return smem_u32(&bars[MX_MAX_STAGES + s]); };
     auto bar_empty = [&](int s) { return smem_u32(&bars[2 * MX_MAX_STAGES + s]); };
@@ -115,14 +117,12 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
 
     const int kblocks = a.K >> 7;                       // 128-wide k blocks
     const int spi = (kblocks + KB - 1) / KB;            // stages per item
-    const int rows_item = a.rows_a;                     // weight rows per A tile = output rows (or SwiGLU columns) per item
     const int n_rows_out = a.dual ? a.inter : a.N;
-    const int ipw = (n_rows_out + rows_item - 1) / rows_item;
+    const int ipw = (n_rows_out + rows_w - 1) / rows_w; // items per work
     const int n_work = a.n_work ? *a.n_work : a.n_work_host;
     const long total = (long)n_work * ipw;
     const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-    const int acc_stride = nt * nd;                     // TMEM columns of one accumulator buffer
-    const int n_acc = (2 * acc_stride <= MX_SF_COL0) ? 2 : 1;
+    const int n_acc = (2 * NW <= MX_SF_COL0) ? 2 : 1;   // accumulator buffers in TMEM columns [0, 256)
 
     if (tid == 0) {
         abort_flag = 0;
@@ -152,31 +152,31 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
         return make_int4(0, wk * nd, rem < nd ? rem : nd, 0);
     };
     const int wk_lo = (int)(lo / ipw), it_lo = (int)(lo - (long)wk_lo * ipw);
+    const uint32_t w_tx = a.a_fmt == MX_A_E2M1 ? w_tile / 2 : w_tile;  // packed FP4 boxes count the bytes actually written
 
     if (lo < hi) {
         if (warp == 0) {
             // ------------------------------------------------ TMA producer (one thread)
             if (lane == 0) {
-                tma_prefetch_desc(&tm_a);
-                tma_prefetch_desc(&tm_b);
+                tma_prefetch_desc(&tm_w);
+                tma_prefetch_desc(&tm_x);
                 int wk = wk_lo, it = it_lo;
                 int4 w = get_work(wk);
                 uint32_t n = 0;
                 for (long item = lo; item < hi && !abort_flag; ++item) {
-                    const int row0 = it * rows_item;
+                    const int row0 = it * rows_w;
                     for (int st = 0; st < spi; ++st, ++n) {
                         const uint32_t s = n % NS, ph = (n / NS) & 1;
                         if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 11)) break;
                         const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
-                        // packed FP4 boxes are counted by the bytes actually written (8 of every 16-byte slot), not by their footprint
-                        const uint32_t a_tx = a.a_fmt == MX_A_E2M1 ? a_box / 2 : a_box;
-                        mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * ((uint32_t)nt * a_tx + b_box));
+                        mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * (x_box + w_tx));
                         const uint32_t dst = smem_u32(ring + (size_t)s * stage_bytes);
                         for (int b = 0; b < nkb; ++b) {
                             const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
-                            tma_load_3d(dst + (uint32_t)b * a_box, &tm_a, kx, row0, w.x, bar_full_ab(s));
-                            if (nt == 2) tma_load_3d(dst + (uint32_t)(KB + b) * a_box, &tm_a, kx, a.inter + row0, w.x, bar_full_ab(s));
-                            tma_load_2d(dst + (uint32_t)(nt * KB) * a_box + (uint32_t)b * b_box, &tm_b, kx, w.y, bar_full_ab(s));
+                            const uint32_t wdst = dst + (uint32_t)KB * x_box + (uint32_t)b * w_tile;
+                            tma_load_3d(wdst, &tm_w, kx, row0, w.x, bar_full_ab(s));
+                            if (a.dual) tma_load_3d(wdst + w_half, &tm_w, kx, a.inter + row0, w.x, bar_full_ab(s));
+                            tma_load_2d(dst + (uint32_t)b * x_box, &tm_x, kx, w.y, bar_full_ab(s));
                         }
                     }
                     if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
@@ -194,11 +194,12 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
             // ------------------------------------------------ MMA issuer (one thread)
             if (lane == 0) {
                 uint32_t n = 0, acc_it = 0;
+                const int b_fmt = a.a_fmt;  // weight format (the B operand); the tokens (A operand) are e4m3
                 for (long item = lo; item < hi && !abort_flag; ++item, ++acc_it) {
                     const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
                     if (!mbar_wait(bar_acc_empty(buf), aph ^ 1, &abort_flag, &g_mx_error, 21)) break;
                     tc_fence_after();
-                    const uint32_t d0 = tmem_base + buf * acc_stride;
+                    const uint32_t d0 = tmem_base + buf * NW;
                     uint32_t accumulate = 0;
                     for (int st = 0; st < spi; ++st, ++n) {
                         const uint32_t s = n % NS, ph = (n / NS) & 1;
@@ -209,18 +210,16 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         const uint32_t sbase = smem_u32(ring + (size_t)s * stage_bytes);
                         const uint32_t sfs = smem_u32(sf_ring + (size_t)s * sf_stage_bytes);
                         for (int b = 0; b < nkb; ++b) {
-                            // scale atoms of this k block -> TMEM: [A tile 0][A tile 1][B], 4 columns each
-                            const uint32_t sfcol = tmem_base + MX_SF_COL0 + (s * KB + b) * (nt + 1) * 4;
-                            if (!(a.dbg & 1) || n == 0) for (int q = 0; q <= nt; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * (nt + 1) + q) * 512u));
-                            const uint64_t da0 = desc_sw128(sbase + (uint32_t)b * a_box);
-                            const uint64_t da1 = desc_sw128(sbase + (uint32_t)(KB + b) * a_box);
-                            const uint64_t db = desc_sw128(sbase + (uint32_t)(nt * KB) * a_box + (uint32_t)b * b_box);
+                            // scale atoms of this k block -> TMEM: [tokens][weights 0][weights 1], 4 columns each
+                            const uint32_t sfcol = tmem_base + MX_SF_COL0 + (s * KB + b) * n_atoms * 4;
+                            if (!(a.dbg & 1) || n == 0)
+                                for (int q = 0; q < n_atoms; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * n_atoms + q) * 512u));
+                            const uint64_t dx = desc_sw128(sbase + (uint32_t)b * x_box);
+                            const uint64_t dw = desc_sw128(sbase + (uint32_t)KB * x_box + (uint32_t)b * w_tile);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {  // 4 MMAs of K = 32: operand descriptors advance by 32 bytes inside the swizzled row
                                 if ((a.dbg & 2) && j > 0) break;
-                                const uint32_t id = mx_idesc(a.a_fmt, nd, j);
-                                tc_mma_mx(d0, da0 + 2 * j, db + 2 * j, id, sfcol, sfcol + nt * 4, accumulate);
-                                if (nt == 2) tc_mma_mx(d0 + nd, da1 + 2 * j, db + 2 * j, id, sfcol + 4, sfcol + nt * 4, accumulate);
+                                tc_mma_mx(d0, dx + 2 * j, dw + 2 * j, mx_idesc(b_fmt, NW, j), sfcol, sfcol + 4, accumulate);
                                 accumulate = 1;
                             }
                         }
@@ -230,21 +229,26 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 }
             }
         } else if (warp >= 8 && warp < 12) {
-            // ------------------------------------------------ scale loaders: thread r = accumulator lane r = tile row r
+            // ------------------------------------------------ scale loaders: thread r feeds token r and weight rows r, r + 128 of the tile.
             // The loads of stage n + PD are in flight while stage n is stored (software pipeline over the flat stage sequence).
             const int r = tid - 256;
             const uint32_t atom_off = (uint32_t)(r & 31) * 16u + (uint32_t)(r >> 5) * 4u;
-            const bool arow = r < a.rows_a;
             struct Cur {
                 long item; int wk, it, st; int4 w;
-                const uint8_t *s_a, *s_b, *s_x; bool brow;
+                const uint8_t *s_0, *s_1, *s_x; bool brow, w0, w1;
+            };
+            auto wrow = [&](int row0, int c) -> int {  // weight row of tile column c
+                if (a.dual) return c < rows_w ? row0 + c : a.inter + row0 + (c - rows_w);
+                return row0 + c;
             };
             auto setup = [&](Cur& c) {
-                const int row0 = c.it * rows_item;
+                const int row0 = c.it * rows_w;
                 const uint8_t* sbase = a.s + (long long)c.w.x * a.s_estride;
-                const int ra = min(row0 + r, a.N - 1), rb = min(a.inter + row0 + r, a.N - 1);
-                c.s_a = sbase + (long)(ra >> a.s_row_shift) * a.s_rstride;
-                c.s_b = sbase + (long)(rb >> a.s_row_shift) * a.s_rstride;
+                c.w0 = r < NW;
+                c.w1 = r + 128 < NW;
+                const int ra = min(wrow(row0, c.w0 ? r : 0), a.N - 1), rb = min(wrow(row0, c.w1 ? r + 128 : 0), a.N - 1);
+                c.s_0 = sbase + (long)(ra >> a.s_row_shift) * a.s_rstride;
+                c.s_1 = sbase + (long)(rb >> a.s_row_shift) * a.s_rstride;
                 c.brow = r < c.w.z;
                 c.s_x = a.xsf + (long)(c.w.y + (c.brow ? r : 0)) * a.xsf_ld;
             };
@@ -264,9 +268,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 for (int b = 0; b < 4; ++b) {
                     if (b >= nkb) break;
                     const int g0 = (kb0 + b) * 4;  // first 32-k group of the k block
-                    v[0][b] = arow ? ldg_stream4(c.s_a + g0) : 0x7F7F7F7Fu;
-                    v[1][b] = (arow && nt == 2) ? ldg_stream4(c.s_b + g0) : 0x7F7F7F7Fu;
-                    v[2][b] = c.brow ? ldg_stream4(c.s_x + g0) : 0x7F7F7F7Fu;
+                    v[0][b] = c.brow ? ldg_stream4(c.s_x + g0) : 0x7F7F7F7Fu;
+                    v[1][b] = c.w0 ? ldg_stream4(c.s_0 + g0) : 0x7F7F7F7Fu;
+                    v[2][b] = c.w1 ? ldg_stream4(c.s_1 + g0) : 0x7F7F7F7Fu;
                 }
             };
             Cur use;
@@ -287,9 +291,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
                         if (b >= nkb) break;
-                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1)) * 512) = q[i][0][b];
-                        if (nt == 2) *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + 1) * 512) = q[i][1][b];
-                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * (nt + 1) + nt) * 512) = q[i][2][b];
+                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * n_atoms) * 512) = q[i][0][b];
+                        *reinterpret_cast<uint32_t*>(sf + (size_t)(b * n_atoms + 1) * 512) = q[i][1][b];
+                        if (n_sfb == 2) *reinterpret_cast<uint32_t*>(sf + (size_t)(b * n_atoms + 2) * 512) = q[i][2][b];
                     }
                     fence_async_smem();
                     mbar_arrive(bar_full_sf(s));
@@ -300,10 +304,10 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 }
             }
         } else if (warp >= 4) {
-            // ------------------------------------------------ epilogue: warps 4-7 and 12-15; warp q (mod 4) reads TMEM lanes
-            // 32 q .. 32 q + 31, the first group takes the even 16-column chunks, the second the odd ones
+            // ------------------------------------------------ epilogue: warps 4-7 and 12-15.  Warp q (mod 4) reads TMEM lanes
+            // 32 q .. 32 q + 31 = tokens; the two groups split the weight-row columns.  A thread owns one token.
             const int q = warp & 3, egrp = warp >= 12 ? 1 : 0;
-            const int r = q * 32 + lane;  // tile row
+            const int t = q * 32 + lane;
             int wk = wk_lo, it = it_lo;
             int4 w = get_work(wk);
             uint32_t acc_it = 0;
@@ -311,71 +315,91 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
                 const bool ready = mbar_wait(bar_acc_full(buf), aph, &abort_flag, &g_mx_error, 41);
                 tc_fence_after();
-                const int row0 = it * rows_item;
-                const bool active = (q * 32 < a.rows_a) && ready;  // warp-uniform
-                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * acc_stride;
-                for (int c0 = egrp * 16; c0 < nd; c0 += 32) {
-                    if (c0 >= w.z) break;  // no tokens in these columns
-                    uint32_t g[16], u[16];
-                    if (active) {
-                        tc_ld16(t0 + c0, g);
-                        if (nt == 2) tc_ld16(t0 + nd + c0, u);
-                        tc_wait_ld();
-                    }
-                    if (!active || (a.dbg & 4)) continue;
-                    // per-column metadata of the chunk, fetched with independent loads before the math
-                    float pw[16];
-                    long orow[16];
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int prow = w.y + min(c0 + c, w.z - 1);
-                        pw[c] = a.pair_w ? __ldg(a.pair_w + prow) : 1.f;
-                        orow[c] = a.pair_out ? (long)__ldg(a.pair_out + prow) : (long)prow;
-                    }
+                const int row0 = it * rows_w;
+                const bool warp_on = ready && q * 32 < w.z && !(a.dbg & 4);  // warp-uniform: some token of this warp exists
+                const bool tok_on = t < w.z;
+                const int prow = w.y + (tok_on ? t : 0);
+                const float pw = (a.pair_w && tok_on) ? __ldg(a.pair_w + prow) : 1.f;
+                const long orow = (a.pair_out && tok_on) ? (long)__ldg(a.pair_out + prow) : (long)prow;
+                const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
+                if (warp_on) {
                     if (a.epi == MX_EPI_SWIGLU_Q8) {
-                        // lane = SwiGLU column row0 + r; the 32 lanes of the warp are one quantisation group (dsv41/fused.py:285-306).
-                        // The 16 token columns of the chunk are processed as 16 independent chains (columns past the work's last
-                        // token compute on garbage and are not stored).
-                        const bool in_range = row0 + r < a.inter;
-                        float h[16], am[16];
+                        // columns c = SwiGLU column row0 + c; 32 consecutive columns are one quantisation group (dsv41/fused.py:285-306)
+                        for (int c0 = egrp * 32; c0 < rows_w; c0 += 64) {
+                            uint32_t g[32], u[32];
+                            tc_ld16(t0 + c0, *reinterpret_cast<uint32_t(*)[16]>(&g[0]));
+                            tc_ld16(t0 + c0 + 16, *reinterpret_cast<uint32_t(*)[16]>(&g[16]));
+                            tc_ld16(t0 + rows_w + c0, *reinterpret_cast<uint32_t(*)[16]>(&u[0]));
+                            tc_ld16(t0 + rows_w + c0 + 16, *reinterpret_cast<uint32_t(*)[16]>(&u[16]));
+                            tc_wait_ld();
+                            if (!tok_on || row0 + c0 >= a.inter) continue;
+                            float h[32], amax = 0.f;
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            float gt = __uint_as_float(g[c]), up = __uint_as_float(u[c]);
-                            if (a.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
-                            h[c] = swiglu_bf16(gt, up, pw[c], a.limit);
-                            am[c] = fabsf(h[c]);
-                        }
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-                            for (int c = 0; c < 16; ++c) am[c] = fmaxf(am[c], __shfl_xor_sync(0xffffffffu, am[c], o));
-                        }
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const float sc = fp8_group_scale_bf16(am[c]);  // am is a bf16 value
+                            for (int c = 0; c < 32; ++c) {
+                                float gt = __uint_as_float(g[c]), up = __uint_as_float(u[c]);
+                                if (a.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
+                                h[c] = swiglu_bf16(gt, up, pw, a.limit);
+                                amax = fmaxf(amax, fabsf(h[c]));
+                            }
+                            const float sc = fp8_group_scale_bf16(amax);  // amax is a bf16 value
                             const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
                             const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact (sc is a power of two)
-                            const float qv = fminf(fmaxf(h[c] * inv, -448.f), 448.f);
-                            if (in_range && c0 + c < w.z) {
-                                reinterpret_cast<uint8_t*>(a.out)[orow[c] * a.out_ld + row0 + r] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
-                                if (lane == 0) a.out_sf[orow[c] * a.out_sf_ld + ((row0 + r) >> 5)] = (uint8_t)sb;
+                            uint32_t o[8];
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                uint32_t v = 0;
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float qv = fminf(fmaxf(h[4 * c + e] * inv, -448.f), 448.f);
+                                    v |= (uint32_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3) << (8 * e);
+                                }
+                                o[c] = v;
                             }
+                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.out) + orow * a.out_ld + row0 + c0);
+                            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                            a.out_sf[orow * a.out_sf_ld + ((row0 + c0) >> 5)] = (uint8_t)sb;
                         }
                     } else {
-                        const bool in_range = row0 + r < a.N;
+                        for (int c0 = egrp * 16; c0 < NW; c0 += 32) {
+                            uint32_t g[16];
+                            tc_ld16(t0 + c0, g);
+                            tc_wait_ld();
+                            if (!tok_on) continue;
+                            const int nrow = row0 + c0;
+                            if (nrow + 16 <= a.N) {
+                                if (a.epi == MX_EPI_STORE_F32) {
+                                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow);
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const float v = __uint_as_float(g[c]) * pw[c];
-                            if (in_range && c0 + c < w.z) {
-                                if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow[c] * a.out_ld + row0 + r] = v;
-                                else if (a.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow[c] * a.out_ld + row0 + r, v);
-                                else reinterpret_cast<__nv_bfloat16*>(a.out)[orow[c] * a.out_ld + row0 + r] = __float2bfloat16_rn(v);
+                                    for (int c = 0; c < 4; ++c)
+                                        dst[c] = make_float4(__uint_as_float(g[4 * c]) * pw, __uint_as_float(g[4 * c + 1]) * pw, __uint_as_float(g[4 * c + 2]) * pw,
+                                                             __uint_as_float(g[4 * c + 3]) * pw);
+                                } else if (a.epi == MX_EPI_ATOMIC_F32) {
+                                    float* dst = reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow;
+#pragma unroll
+                                    for (int c = 0; c < 16; ++c) atomicAdd(dst + c, __uint_as_float(g[c]) * pw);
+                                } else {
+                                    uint32_t o[8];
+#pragma unroll
+                                    for (int c = 0; c < 8; ++c)
+                                        o[c] = f32_to_bf16_bits(__uint_as_float(g[2 * c]) * pw) | (f32_to_bf16_bits(__uint_as_float(g[2 * c + 1]) * pw) << 16);
+                                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.out_ld + nrow);
+                                    dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                                    dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                                }
+                            } else {  // ragged last tile
+                                for (int c = 0; c < 16 && nrow + c < a.N; ++c) {
+                                    const float v = __uint_as_float(g[c]) * pw;
+                                    if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + nrow + c] = v;
+                                    else if (a.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow + c, v);
+                                    else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + nrow + c] = __float2bfloat16_rn(v);
+                                }
                             }
                         }
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(bar_acc_empty(buf));  // 128 epilogue threads: the accumulator buffer may be overwritten
+                mbar_arrive(bar_acc_empty(buf));  // 256 epilogue threads: the accumulator buffer may be overwritten
                 if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
             }
         }
@@ -424,26 +448,29 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     if (a.a_fmt != MX_A_E2M1 && a.a_fmt != MX_A_E4M3) return ERR_UNSUPPORTED;
     if (a.K <= 0 || a.K % 128 || a.N <= 0) return ERR_BAD_SHAPE;
     if (a.nd < 16 || a.nd > 128 || a.nd % 16) return ERR_BAD_SHAPE;
-    if (a.rows_a != 32 && a.rows_a != 64 && a.rows_a != 128) return ERR_BAD_SHAPE;
+    if (a.rows_a != 32 && a.rows_a != 64 && a.rows_a != 128 && !(a.rows_a == 256 && !a.dual)) return ERR_BAD_SHAPE;
     if (a.dual && (a.epi != MX_EPI_SWIGLU_Q8 || a.inter <= 0 || a.inter % 32 || a.N != 2 * a.inter || !a.out_sf)) return ERR_BAD_SHAPE;
     if (!a.dual && a.epi == MX_EPI_SWIGLU_Q8) return ERR_BAD_SHAPE;
     if (((uintptr_t)a.w & 31) || (a.w_estride & 31) || ((uintptr_t)a.x8 & 15) || ((uintptr_t)a.s & 3) || (a.s_rstride & 3) || (a.s_estride & 3) ||
         ((uintptr_t)a.xsf & 3) || (a.xsf_ld & 3))
         return ERR_BAD_ALIGN;
+    if (a.epi == MX_EPI_SWIGLU_Q8 && (((uintptr_t)a.out & 15) || (a.out_ld & 15))) return ERR_BAD_ALIGN;
+    if ((a.epi == MX_EPI_STORE_F32 || a.epi == MX_EPI_STORE_BF16) && (((uintptr_t)a.out & 15) || (a.out_ld & 7))) return ERR_BAD_ALIGN;
     if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
-    const int nt = a.dual ? 2 : 1;
+    const int NW = a.dual ? 2 * a.rows_a : a.rows_a;
+    const int n_atoms = 1 + (NW + 127) / 128;
     // pipeline geometry: as many 128-wide k blocks per stage as still leave a ring of at least 3 stages
-    const size_t slack = 1024 + 16384;  // the A descriptors always span 128 rows: slack behind the ring for tiles that fetch fewer rows
+    const size_t slack = 1024 + 16384;  // the token descriptors always span 128 rows: slack behind the ring for boxes with fewer rows
     if (a.kb < 1 || a.kb > 4) a.kb = 4;
     int stages = 0;
     size_t stage = 0, sf_stage = 0;
     for (;; --a.kb) {
-        stage = (size_t)(nt * a.kb) * a.rows_a * 128 + (size_t)a.kb * a.nd * 128;
-        sf_stage = (size_t)a.kb * (nt + 1) * 512;
+        stage = (size_t)a.kb * ((size_t)a.nd * 128 + (size_t)NW * 128);
+        sf_stage = (size_t)a.kb * n_atoms * 512;
         stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
         if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
-        // scale columns in TMEM: stages * kb * (nt + 1) * 4 <= 256
-        while (stages > 1 && stages * a.kb * (nt + 1) * 4 > MX_TMEM_COLS - MX_SF_COL0) --stages;
+        // scale columns in TMEM: stages * kb * n_atoms * 4 <= 256
+        while (stages > 1 && stages * a.kb * n_atoms * 4 > MX_TMEM_COLS - MX_SF_COL0) --stages;
         if (stages >= 3 || a.kb == 1) break;
     }
     if (stages < 2) return ERR_BAD_SHAPE;

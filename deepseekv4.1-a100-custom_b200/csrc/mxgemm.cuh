@@ -36,9 +36,9 @@ struct MxArgs {
     const int* n_work;
     int n_work_host;
     int dense_rows;
-    int nd;                 // token columns per work = N of the tensor-core tile (multiple of 16, <= 128)
-    int rows_a;             // weight rows fetched per A tile (32, 64 or 128); the tile always spans 128 accumulator lanes
-    int dual;               // 1: two A tiles per item (gate rows r and up rows inter + r), epilogue SWIGLU
+    int nd;                 // tokens per work = token rows fetched per tile (multiple of 16, <= 128; the tile spans 128 accumulator lanes)
+    int rows_a;             // weight rows per tile half: the MMA covers rows_a (single) or 2 * rows_a (dual) weight rows
+    int dual;               // 1: gate rows r and up rows inter + r side by side in one tile, epilogue SWIGLU
     int kb;                 // 128-wide k blocks per pipeline stage
     int n_stages;
     int epi;

@@ -184,7 +184,8 @@ int b200_mx_quantize_rows(const void* x, long long x_ld, const int* src_row, int
  *   epilogue 1: N = 2*inter, out e4m3 [.., inter] + out_sf E8M0 [.., inter/32] = FP8 quantisation of
  *               bf16(pair_w * silu(min(g, limit)) * clamp(u, +-limit)), g = rows 0..inter-1, u = rows inter..2*inter-1
  *               (dsv41/fused.py:285-306); round_gu_bf16 rounds g, u to bf16 first (shared expert).
- *   tokens_per_work: 16..128, multiple of 16 (N of the tensor-core tile); rows_per_tile: 32, 64 or 128 weight rows per tile.
+ *   tokens_per_work: 16..128, multiple of 16 (the tokens are the M side of the tensor-core tile); rows_per_tile: weight rows per
+ *   tile on the N side: 32, 64, 128 or (epilogues 0, 2) 256; epilogue 1 pairs rows_per_tile gate rows with as many up rows.
  *   K % 128 == 0; w 32-byte aligned; workspace b200_mx_grouped_workspace_bytes(n_rows) bytes when groups are given. */
 size_t b200_mx_grouped_workspace_bytes(int n_rows);
 int b200_mx_grouped_gemm(const void* w, long long w_estride, const void* s, long long s_estride, int s_cols, int fmt, int n_local_experts, int N, int K,

@@ -51,7 +51,27 @@ def test_mx_grouped_store(mods, oracle, dev, G, M, N, K, rows):
     assert rel_err(y, ref) < 2e-3
 
 
-def test_mx_grouped_swiglu_epilogue(mods, oracle, dev):
+@pytest.mark.parametrize("M,N,K,rows,tpw", [(100, 512, 512, 256, 128), (70, 256, 1024, 128, 64), (33, 768, 256, 256, 32)])
+def test_mx_grouped_wide_tiles(mods, oracle, dev, M, N, K, rows, tpw):
+    E, G = 5, 2
+    w, s, g = _experts(E, N, K, M + rows)
+    x = (torch.randn(G * M, K, generator=g) * 2).to(torch.bfloat16)
+    q8, sf = mods.cukern.mx_quantize_rows(x.to(dev))
+    xq = oracle.fake_quant_fp8(x, 32)
+    experts = torch.tensor([4, 1], dtype=torch.int32)
+    grp_start = torch.arange(0, G * M + 1, M, dtype=torch.int32)
+    P = G * M
+    wt = torch.rand(P, generator=g)
+    out_rows = torch.randperm(P, generator=g).int()
+    ref = oracle.fp4_pairs(xq, w, s, experts.repeat_interleave(M), torch.arange(P), out_rows, wt, P)
+    y = mods.cukern.mx_grouped(w.to(dev), s.to(dev), q8, sf, experts.to(dev), grp_start.to(dev), None, out_rows.to(dev), wt.to(dev), P, rows_per_tile=rows,
+                               tokens_per_work=tpw)
+    assert mods.cukern.device_error(dev) == 0
+    assert rel_err(y, ref) < 2e-3
+
+
+@pytest.mark.parametrize("rows,tpw", [(32, 16), (64, 32), (128, 128)])
+def test_mx_grouped_swiglu_epilogue(mods, oracle, dev, rows, tpw):
     E, inter, K, G, M = 4, 256, 512, 3, 7
     w, s, g = _experts(E, 2 * inter, K, 77, 112, 120)
     x = torch.randn(G * M, K, generator=g).to(torch.bfloat16)
@@ -65,7 +85,7 @@ def test_mx_grouped_swiglu_epilogue(mods, oracle, dev):
     for limit in (10.0, 0.0):
         ref = oracle.swiglu_quant(gu, wt, inter, limit)
         h8, hsf = mods.cukern.mx_grouped(w.to(dev), s.to(dev), q8, sf, experts.to(dev), grp_start.to(dev), None, None, wt.to(dev), P, epilogue="swiglu_q8",
-                                         limit=limit)
+                                         limit=limit, rows_per_tile=rows, tokens_per_work=tpw)
         assert mods.cukern.device_error(dev) == 0
         h = _deq(h8.cpu(), hsf.cpu())
         # isolated elements may sit on a rounding boundary (fp32 summation order differs): compare values, not bits
