@@ -5,11 +5,13 @@
 // tcgen05.mma.kind::mxf8f6f4.block_scale, so the weights go HBM -> TMA -> shared memory -> tensor core with no
 // arithmetic on the way, and the accumulators live in tensor memory (TMEM) in fp32.
 //
-// The weights are the M side of the tile (128 accumulator lanes = weight rows), the tokens of a work (<= nd) are the N side.
-// Warp roles of the persistent CTA:
+// The tokens of a work (<= 128) are the M side of the tile (accumulator lanes), up to 256 weight rows are the N side: a
+// 128 x 256 x 32 MMA runs in about 137 clocks, less than the fixed cost of issuing it and of handing a pipeline stage over, so
+// every instruction and every stage carries as many weight bytes as it can.  Warp roles of the persistent CTA:
 //   warp 0      TMA producer: boxes of the weight tile(s) and of the activation rows into a shared-memory ring
 //   warp 1      allocates TMEM; one thread copies the scale atoms into TMEM (tcgen05.cp) and issues the MMAs
-//   warps 4-7, 12-15  epilogue: tcgen05.ld of the accumulator lanes of their TMEM sub-partition, SwiGLU + FP8 quantisation or store
+//   warps 4-7, 12-15  epilogue: a thread owns one token (TMEM lane) and reads its accumulator row with tcgen05.ld; SwiGLU + FP8
+//               quantisation or store; the two groups split the columns
 //   warps 8-11  scale loaders: one thread per tile row builds the 32x4x4 scale atoms in shared memory
 // Every wait is bounded; a wait that runs out of time records a code in a device error word and the CTA runs to its end.
 //
@@ -17,7 +19,6 @@
 // fp4_tcw.cu, expert_chain.cu for decode) when the activation is FP8-quantised, which it always is inside the MoE layer
 // (dsv41/model.py:2040, dsv41/fused.py:297-306).
 #include <cuda_fp8.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "mxgemm.cuh"
@@ -122,18 +123,19 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     const int n_work = a.n_work ? *a.n_work : a.n_work_host;
     const long total = (long)n_work * ipw;
     const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-    const int n_acc = (2 * NW <= MX_SF_COL0) ? 2 : 1;   // accumulator buffers in TMEM columns [0, 256)
+    const int n_acc = (2 * NW <= MX_ACC_COLS_MAX) ? 2 : 1;  // two accumulator buffers (epilogue overlaps the next item) when they fit
+    const uint32_t sf_col0 = (uint32_t)(n_acc * NW);        // the scale columns follow the accumulators
 
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < NS; ++s) {
             mbar_init(bar_full_ab(s), 1);
-            mbar_init(bar_full_sf(s), 128);
+            mbar_init(bar_full_sf(s), 4);     // one arrival per scale-loader warp
             mbar_init(bar_empty(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full(b), 1);
-            mbar_init(bar_acc_empty(b), 256);
+            mbar_init(bar_acc_empty(b), 8);   // one arrival per epilogue warp
         }
         mbar_fence_init();
     }
@@ -160,26 +162,32 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
             if (lane == 0) {
                 tma_prefetch_desc(&tm_w);
                 tma_prefetch_desc(&tm_x);
-                int wk = wk_lo, it = it_lo;
-                int4 w = get_work(wk);
+                // flat sequence of stages (item, k range)
+                struct PCur { long item; int wk, it, st; int4 w; };
+                auto advance = [&](PCur& c) {
+                    if (++c.st < spi) return;
+                    c.st = 0;
+                    ++c.item;
+                    if (++c.it == ipw) { c.it = 0; ++c.wk; if (c.item < hi) c.w = get_work(c.wk); }
+                };
+                PCur cur{lo, wk_lo, it_lo, 0, get_work(wk_lo)};
                 uint32_t n = 0;
-                for (long item = lo; item < hi && !abort_flag; ++item) {
-                    const int row0 = it * rows_w;
-                    for (int st = 0; st < spi; ++st, ++n) {
-                        const uint32_t s = n % NS, ph = (n / NS) & 1;
-                        if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 11)) break;
-                        const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
-                        mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * (x_box + w_tx));
-                        const uint32_t dst = smem_u32(ring + (size_t)s * stage_bytes);
-                        for (int b = 0; b < nkb; ++b) {
-                            const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
-                            const uint32_t wdst = dst + (uint32_t)KB * x_box + (uint32_t)b * w_tile;
-                            tma_load_3d(wdst, &tm_w, kx, row0, w.x, bar_full_ab(s));
-                            if (a.dual) tma_load_3d(wdst + w_half, &tm_w, kx, a.inter + row0, w.x, bar_full_ab(s));
-                            tma_load_2d(dst + (uint32_t)b * x_box, &tm_x, kx, w.y, bar_full_ab(s));
-                        }
+                for (; cur.item < hi && !abort_flag; ++n) {
+                    const int4 w = cur.w;
+                    const int row0 = cur.it * rows_w, st = cur.st;
+                    const uint32_t s = n % NS, ph = (n / NS) & 1;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 11)) break;
+                    const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
+                    mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * (x_box + w_tx));
+                    const uint32_t dst = smem_u32(ring + (size_t)s * stage_bytes);
+                    for (int b = 0; b < nkb; ++b) {
+                        const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
+                        const uint32_t wdst = dst + (uint32_t)KB * x_box + (uint32_t)b * w_tile;
+                        tma_load_3d(wdst, &tm_w, kx, row0, w.x, bar_full_ab(s));
+                        if (a.dual) tma_load_3d(wdst + w_half, &tm_w, kx, a.inter + row0, w.x, bar_full_ab(s));
+                        tma_load_2d(dst + (uint32_t)b * x_box, &tm_x, kx, w.y, bar_full_ab(s));
                     }
-                    if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
+                    advance(cur);
                 }
                 // every load issued above must have landed before the CTA may exit
                 for (int k = 0; k < NS && k < (int)n; ++k) {
@@ -211,14 +219,12 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         const uint32_t sfs = smem_u32(sf_ring + (size_t)s * sf_stage_bytes);
                         for (int b = 0; b < nkb; ++b) {
                             // scale atoms of this k block -> TMEM: [tokens][weights 0][weights 1], 4 columns each
-                            const uint32_t sfcol = tmem_base + MX_SF_COL0 + (s * KB + b) * n_atoms * 4;
-                            if (!(a.dbg & 1) || n == 0)
-                                for (int q = 0; q < n_atoms; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * n_atoms + q) * 512u));
+                            const uint32_t sfcol = tmem_base + sf_col0 + (s * KB + b) * n_atoms * 4;
+                            for (int q = 0; q < n_atoms; ++q) tc_cp_sf(sfcol + q * 4, desc_sf_atom(sfs + (uint32_t)(b * n_atoms + q) * 512u));
                             const uint64_t dx = desc_sw128(sbase + (uint32_t)b * x_box);
                             const uint64_t dw = desc_sw128(sbase + (uint32_t)KB * x_box + (uint32_t)b * w_tile);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {  // 4 MMAs of K = 32: operand descriptors advance by 32 bytes inside the swizzled row
-                                if ((a.dbg & 2) && j > 0) break;
                                 tc_mma_mx(d0, dx + 2 * j, dw + 2 * j, mx_idesc(b_fmt, NW, j), sfcol, sfcol + 4, accumulate);
                                 accumulate = 1;
                             }
@@ -296,7 +302,8 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         if (n_sfb == 2) *reinterpret_cast<uint32_t*>(sf + (size_t)(b * n_atoms + 2) * 512) = q[i][2][b];
                     }
                     fence_async_smem();
-                    mbar_arrive(bar_full_sf(s));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full_sf(s));  // arrivals on one barrier serialise: one per warp, not one per thread
                     advance(use);
                     ++n;
                     load(ld, q[i]);
@@ -316,7 +323,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 const bool ready = mbar_wait(bar_acc_full(buf), aph, &abort_flag, &g_mx_error, 41);
                 tc_fence_after();
                 const int row0 = it * rows_w;
-                const bool warp_on = ready && q * 32 < w.z && !(a.dbg & 4);  // warp-uniform: some token of this warp exists
+                const bool warp_on = ready && q * 32 < w.z;  // warp-uniform: some token of this warp exists
                 const bool tok_on = t < w.z;
                 const int prow = w.y + (tok_on ? t : 0);
                 const float pw = (a.pair_w && tok_on) ? __ldg(a.pair_w + prow) : 1.f;
@@ -399,7 +406,8 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                     }
                 }
                 tc_fence_before();
-                mbar_arrive(bar_acc_empty(buf));  // 256 epilogue threads: the accumulator buffer may be overwritten
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty(buf));  // the accumulator buffer may be overwritten once all 8 warps have read it
                 if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
             }
         }
@@ -443,12 +451,11 @@ static int make_tmap(CUtensorMap* tm, CUtensorMapDataType dt, int rank, const vo
 
 int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     MxArgs a = a_in;
-    if (const char* e = getenv("B200_MX_DBG")) a.dbg = atoi(e);
     if (!a.w || !a.s || !a.x8 || !a.xsf || !a.out) return ERR_BAD_ARG;
     if (a.a_fmt != MX_A_E2M1 && a.a_fmt != MX_A_E4M3) return ERR_UNSUPPORTED;
     if (a.K <= 0 || a.K % 128 || a.N <= 0) return ERR_BAD_SHAPE;
     if (a.nd < 16 || a.nd > 128 || a.nd % 16) return ERR_BAD_SHAPE;
-    if (a.rows_a != 32 && a.rows_a != 64 && a.rows_a != 128 && !(a.rows_a == 256 && !a.dual)) return ERR_BAD_SHAPE;
+    if (a.rows_a < 32 || a.rows_a % 32 || a.rows_a * (a.dual ? 2 : 1) > 256) return ERR_BAD_SHAPE;
     if (a.dual && (a.epi != MX_EPI_SWIGLU_Q8 || a.inter <= 0 || a.inter % 32 || a.N != 2 * a.inter || !a.out_sf)) return ERR_BAD_SHAPE;
     if (!a.dual && a.epi == MX_EPI_SWIGLU_Q8) return ERR_BAD_SHAPE;
     if (((uintptr_t)a.w & 31) || (a.w_estride & 31) || ((uintptr_t)a.x8 & 15) || ((uintptr_t)a.s & 3) || (a.s_rstride & 3) || (a.s_estride & 3) ||
@@ -459,7 +466,8 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
     const int NW = a.dual ? 2 * a.rows_a : a.rows_a;
     const int n_atoms = 1 + (NW + 127) / 128;
-    // pipeline geometry: as many 128-wide k blocks per stage as still leave a ring of at least 3 stages
+    // pipeline geometry: every stage costs a fixed round of barrier hand-offs, so stages are made as fat as a ring of two allows
+    // (measured: two k blocks per stage, two stages beat one k block per stage, four or five stages)
     const size_t slack = 1024 + 16384;  // the token descriptors always span 128 rows: slack behind the ring for boxes with fewer rows
     if (a.kb < 1 || a.kb > 4) a.kb = 4;
     int stages = 0;
@@ -470,8 +478,8 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
         stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
         if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
         // scale columns in TMEM: stages * kb * n_atoms * 4 <= 256
-        while (stages > 1 && stages * a.kb * n_atoms * 4 > MX_TMEM_COLS - MX_SF_COL0) --stages;
-        if (stages >= 3 || a.kb == 1) break;
+        while (stages > 1 && stages * a.kb * n_atoms * 4 > MX_TMEM_COLS - (2 * NW <= MX_ACC_COLS_MAX ? 2 : 1) * NW) --stages;
+        if (stages >= 2 || a.kb == 1) break;
     }
     if (stages < 2) return ERR_BAD_SHAPE;
     a.n_stages = stages;

@@ -8,7 +8,7 @@ namespace b200 {
 
 constexpr int MX_THREADS = 512;   // 16 warps: TMA producer, MMA issuer, 2 spare, 4 epilogue, 4 scale loaders, 4 more epilogue
 constexpr int MX_TMEM_COLS = 512;
-constexpr int MX_SF_COL0 = 256;   // scale factors live in TMEM columns [256, 512)
+constexpr int MX_ACC_COLS_MAX = 384;  // TMEM columns the accumulator buffers may take; the rest holds the scale factors
 constexpr int MX_MAX_STAGES = 8;
 constexpr int MX_SMEM_LIMIT = 227 * 1024 - 2048;
 
@@ -51,7 +51,6 @@ struct MxArgs {
     float limit;
     int inter;
     int round_gu_bf16;
-    int dbg;                // timing experiments only
 };
 
 int mx_launch(const MxArgs& a, cudaStream_t stream);

@@ -84,11 +84,12 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 // Bounded wait on an mbarrier phase.  `abort_flag` (shared memory) short-circuits every later wait of the CTA once one
 // wait has run out of time, so the CTA still runs to its end (barriers stay matched) and returns; `where` is recorded in
 // the device error word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err_word, int where) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err_word, int where, unsigned backoff_ns = 0) {
     if (*abort_flag) return false;
     unsigned long long t0 = 0;
     for (uint32_t i = 0;; ++i) {
         if (mbar_test(bar, parity)) return true;
+        if (backoff_ns) __nanosleep(backoff_ns);  // roles off the critical path leave the issue slots to the others
         if ((i & 255u) == 255u) {
             if (*abort_flag) return false;
             unsigned long long t = global_timer_ns();
