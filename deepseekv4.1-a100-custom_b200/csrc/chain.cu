@@ -1,6 +1,6 @@
 // MoE layer for a decode batch and the C-ABI entry points of the grouped FP4 / dense FP8 GEMMs.
 //
-// Layer = one routing kernel (input fake quantisation, router, stable bucketing of the (token, expert) pairs by expert,
+// Layer = one routing kernel (input fake quantisation, router, bucketing of the (token, expert) pairs by expert,
 // work list) followed by the weight-streaming skinny GEMMs (skinny.cu) with fused epilogues and a final combine.
 #include "common.cuh"
 #include "skinny.cuh"
@@ -38,16 +38,17 @@ struct RouteArgs {
 };
 
 // One block per token: fake-quantise the token's activation (dsv41/quant.py:46-54; one thread per group of 32, four 16-byte
-// loads in flight) and route it (dsv41/model.py:1614-1630).  The last block to finish buckets all pairs by expert (stable, the
-// order of dsv41/moe_kernels.py:111-116 and dsv41/decode.py:417-433) and emits the work list of the shard's experts.
+// loads in flight) and route it (dsv41/model.py:1614-1630).  The last block to finish buckets all pairs by expert (the
+// grouping of dsv41/moe_kernels.py:111-116 and dsv41/decode.py:417-433; the order inside an expert is free) and emits the work list of
+// the shard's experts.
 __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArgs a) {
-    __shared__ float sh_f[8];
-    __shared__ int sh_i[4];
+    __shared__ float s_val[ROUTE_MAX_EXPERTS], s_key[ROUTE_MAX_EXPERTS];  // router scratch of warp 0
     __shared__ int is_last;
     __shared__ int s_eid[ROUTE_MAX_PAIRS];
     __shared__ int s_cnt[ROUTE_MAX_EXPERTS];
     __shared__ int s_start[ROUTE_MAX_EXPERTS];
     __shared__ int s_woff[ROUTE_MAX_EXPERTS];
+    __shared__ int s_cur[ROUTE_MAX_EXPERTS];
     __shared__ int s_wtot[2][ROUTE_THREADS / 32];
     const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
@@ -76,8 +77,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
             for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
     }
-    gate_topk_row(a.logits_f32 ? a.logits_f32 + (long)tok * a.E : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.E : nullptr, a.bias, a.E,
-                  a.temp, a.topk, a.route_scale, a.mode, a.norm, a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, sh_f, sh_i);
+    if (warp == 0)
+        gate_topk_warp(a.logits_f32 ? a.logits_f32 + (long)tok * a.E : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.E : nullptr, a.bias, a.E,
+                       a.temp, a.topk, a.route_scale, a.mode, a.norm, a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
     if (a.no_bucket) return;
     __threadfence();
     __syncthreads();
@@ -130,30 +132,26 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
         }
     }
     __syncthreads();
-    // stable placement: one warp per expert walks the pairs 32 at a time (ballot + prefix popcount keeps the pair order)
-    for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+    // works of this shard's experts, then the placement of the pairs through one cursor per expert.  The order of the pairs
+    // inside an expert is whatever the atomics give: every pair is computed on its own and lands in its own output slot, so
+    // the order does not reach the results.
+    for (int e = tid; e < E; e += ROUTE_THREADS) {
         const int cnt = s_cnt[e];
-        if (cnt == 0) continue;
-        int pos = s_start[e];
-        for (int base = 0; base < P; base += 32) {
-            const int p = base + lane;
-            const bool hit = p < P && s_eid[p] == e;
-            const unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                const int o = pos + __popc(m & ((1u << lane) - 1u));
-                a.pair_tok[o] = p / a.topk;
-                a.pair_out[o] = p;
-                a.pair_w[o] = __ldcg(a.wt + p);
-            }
-            pos += __popc(m);
-        }
-        if (e >= a.shard_start && e < a.shard_start + a.shard_n) {
+        s_cur[e] = s_start[e];
+        if (cnt > 0 && e >= a.shard_start && e < a.shard_start + a.shard_n) {
             const int nsub = (cnt + a.tpw - 1) / a.tpw;
-            for (int i = lane; i < nsub; i += 32) {
+            for (int i = 0; i < nsub; ++i) {
                 const int rem = cnt - i * a.tpw;
                 a.work[s_woff[e] + i] = make_int4(e - a.shard_start, s_start[e] + i * a.tpw, rem < a.tpw ? rem : a.tpw, e);
             }
         }
+    }
+    __syncthreads();
+    for (int p = tid; p < P; p += ROUTE_THREADS) {
+        const int o = atomicAdd(&s_cur[s_eid[p]], 1);
+        a.pair_tok[o] = p / a.topk;
+        a.pair_out[o] = p;
+        a.pair_w[o] = __ldcg(a.wt + p);
     }
 }
 
@@ -457,12 +455,18 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         g2.pair_out = w.pair_out; g2.out = small ? w.y2 : w.acc; g2.out_ld = D;
         if ((rc = mx_launch(g2, stream))) return rc;
         if (shared) {
+            // one matrix, few works: tiles small enough that (works x tiles) still covers the SMs
+            const int works_s = (T + nd - 1) / nd;
+            int rows1s = 128;
+            while (rows1s > 32 && (long)works_s * (I / rows1s) < 148) rows1s >>= 1;
+            int rows2s = 256;
+            while (rows2s > 32 && (long)works_s * (D / rows2s) < 148) rows2s >>= 1;
             MxArgs s1{};
             s1.w = m->sh_w13; s1.n_experts = 1; s1.a_fmt = MX_A_E4M3;
             s1.s = (const uint8_t*)m->sh_s13; s1.s_rstride = m->sh_s13_cols; s1.s_row_shift = 5;
             s1.N = 2 * I; s1.K = D; s1.x8 = w.x8t; s1.x8_rows = T + 128; s1.xsf = w.xsft; s1.xsf_ld = D / 32;
             s1.work = nullptr; s1.dense_rows = T; s1.n_work_host = (T + nd - 1) / nd;
-            s1.nd = nd; s1.rows_a = rows1; s1.dual = 1; s1.kb = 4; s1.epi = MX_EPI_SWIGLU_Q8;
+            s1.nd = nd; s1.rows_a = rows1s; s1.dual = 1; s1.kb = 4; s1.epi = MX_EPI_SWIGLU_Q8;
             s1.out = w.hs8; s1.out_ld = I; s1.out_sf = w.hssf; s1.out_sf_ld = I / 32; s1.limit = m->swiglu_limit; s1.inter = I; s1.round_gu_bf16 = 1;
             if ((rc = mx_launch(s1, stream))) return rc;
             MxArgs s2{};
@@ -470,7 +474,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             s2.s = (const uint8_t*)m->sh_s2; s2.s_rstride = m->sh_s2_cols; s2.s_row_shift = 5;
             s2.N = D; s2.K = I; s2.x8 = w.hs8; s2.x8_rows = T + 128; s2.xsf = w.hssf; s2.xsf_ld = I / 32;
             s2.work = nullptr; s2.dense_rows = T; s2.n_work_host = (T + nd - 1) / nd;
-            s2.nd = nd; s2.rows_a = rows2; s2.dual = 0; s2.kb = 4; s2.epi = MX_EPI_STORE_BF16;
+            s2.nd = nd; s2.rows_a = rows2s; s2.dual = 0; s2.kb = 4; s2.epi = MX_EPI_STORE_BF16;
             s2.out = w.ys; s2.out_ld = D;
             if ((rc = mx_launch(s2, stream))) return rc;
         }

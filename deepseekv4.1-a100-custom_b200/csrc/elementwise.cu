@@ -18,13 +18,15 @@ __global__ void fake_quant_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_
     y[g * 32 + lane] = __float2bfloat16_rn(fp8_fake_quant_value(v, s));
 }
 
-__global__ void __launch_bounds__(GATE_THREADS) gate_topk_kernel(const float* __restrict__ scores, const float* __restrict__ bias, int E, float temp,
-                                                                 int topk, float route_scale, int mode, int norm, int* __restrict__ eid,
-                                                                 float* __restrict__ wt) {
-    __shared__ float sh_f[8];
-    __shared__ int sh_i[4];
-    long row = blockIdx.x;
-    gate_topk_row(scores + row * E, nullptr, bias, E, temp, topk, route_scale, mode, norm, eid + row * topk, wt + row * topk, sh_f, sh_i);
+__global__ void __launch_bounds__(32 * GATE_ROWS_PER_BLOCK) gate_topk_kernel(const float* __restrict__ scores, const float* __restrict__ bias, int rows,
+                                                                             int E, float temp, int topk, float route_scale, int mode, int norm,
+                                                                             int* __restrict__ eid, float* __restrict__ wt) {
+    extern __shared__ float gate_smem[];  // per warp: E scores + E keys
+    const int warp = threadIdx.x >> 5;
+    const long row = (long)blockIdx.x * GATE_ROWS_PER_BLOCK + warp;
+    if (row >= rows) return;
+    float* s_val = gate_smem + (size_t)warp * 2 * E;
+    gate_topk_warp(scores + row * E, nullptr, bias, E, temp, topk, route_scale, mode, norm, eid + row * topk, wt + row * topk, s_val, s_val + E);
 }
 
 // ------------------------------------------------------------------ swiglu_quant  (dsv41/fused.py:285-316)
@@ -102,10 +104,12 @@ extern "C" int b200_fake_quant_fp8(const void* x, void* y, long long n_elems, cu
 extern "C" int b200_gate_topk(const float* scores, const float* bias, int rows, int n_experts, float temp, int topk, float route_scale,
                               int score_mode, int norm, int* eid, float* wt, cudaStream_t stream) {
     if (!scores || !eid || !wt || rows < 0) return ERR_BAD_ARG;
-    if (n_experts < 1 || n_experts > GATE_THREADS * GATE_MAX_PER_THREAD || topk < 1 || topk > n_experts || topk > 32) return ERR_BAD_SHAPE;
+    if (n_experts < 1 || n_experts > GATE_MAX_EXPERTS || topk < 1 || topk > n_experts || topk > 32) return ERR_BAD_SHAPE;
     if (score_mode < 0 || score_mode > 2) return ERR_UNSUPPORTED;
     if (rows == 0) return 0;
-    gate_topk_kernel<<<rows, GATE_THREADS, 0, stream>>>(scores, bias, n_experts, temp, topk, route_scale, score_mode, norm, eid, wt);
+    const size_t smem = (size_t)GATE_ROWS_PER_BLOCK * 2 * n_experts * sizeof(float);
+    gate_topk_kernel<<<(rows + GATE_ROWS_PER_BLOCK - 1) / GATE_ROWS_PER_BLOCK, 32 * GATE_ROWS_PER_BLOCK, smem, stream>>>(scores, bias, rows, n_experts, temp, topk,
+                                                                                                                  route_scale, score_mode, norm, eid, wt);
     B200_CHECK_LAUNCH();
     return 0;
 }

@@ -60,6 +60,9 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -384,7 +387,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                                 } else if (a.epi == MX_EPI_ATOMIC_F32) {
                                     float* dst = reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow;
 #pragma unroll
-                                    for (int c = 0; c < 16; ++c) atomicAdd(dst + c, __uint_as_float(g[c]) * pw);
+                                    for (int c = 0; c < 4; ++c)  // one 16-byte reduction instead of four scalar ones
+                                        red_add_v4(dst + 4 * c, __uint_as_float(g[4 * c]) * pw, __uint_as_float(g[4 * c + 1]) * pw,
+                                                   __uint_as_float(g[4 * c + 2]) * pw, __uint_as_float(g[4 * c + 3]) * pw);
                                 } else {
                                     uint32_t o[8];
 #pragma unroll
@@ -436,6 +441,45 @@ __global__ void mx_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, lon
     if (lane == 0) sf[(long)row * gpr + grp] = (uint8_t)((f32_as_u32(s) >> 23) & 0xFFu);
 }
 
+// 16-byte-aligned rows: a thread quantises 8 values (one 16-byte load), 4 threads share a group of 32
+__global__ void __launch_bounds__(256) mx_quantize_rows_vec_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const int* __restrict__ src_row,
+                                                                   int rows, int K, uint8_t* __restrict__ q8, uint8_t* __restrict__ sf) {
+    const int tpr = K >> 3;  // threads per row
+    const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool on = gid < (long)rows * tpr;  // K % 32 == 0: the 4 threads of a group are on or off together
+    const int row = on ? (int)(gid / tpr) : 0, c8 = on ? (int)(gid % tpr) : 0;
+    const long src = src_row ? __ldg(src_row + row) : row;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (on) raw = __ldg(reinterpret_cast<const uint4*>(x + src * x_ld) + c8);
+    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8], amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = bf16_bits_to_f32(u[i] & 0xFFFFu);
+        v[2 * i + 1] = bf16_bits_to_f32(u[i] >> 16);
+        amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!on) return;
+    const float sc = fp8_group_scale_bf16(amax);  // the inputs are bf16 values
+    const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
+    const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact
+    uint32_t o[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float qv = fminf(fmaxf(v[4 * h + e] * inv, -448.f), 448.f);
+            w |= (uint32_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3) << (8 * e);
+        }
+        o[h] = w;
+    }
+    *reinterpret_cast<uint2*>(q8 + (long)row * K + c8 * 8) = make_uint2(o[0], o[1]);
+    if ((c8 & 3) == 0) sf[(long)row * (K >> 5) + (c8 >> 2)] = (uint8_t)sb;
+}
+
 // ------------------------------------------------------------------ host side
 int sm_count();
 
@@ -462,7 +506,7 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
         ((uintptr_t)a.xsf & 3) || (a.xsf_ld & 3))
         return ERR_BAD_ALIGN;
     if (a.epi == MX_EPI_SWIGLU_Q8 && (((uintptr_t)a.out & 15) || (a.out_ld & 15))) return ERR_BAD_ALIGN;
-    if ((a.epi == MX_EPI_STORE_F32 || a.epi == MX_EPI_STORE_BF16) && (((uintptr_t)a.out & 15) || (a.out_ld & 7))) return ERR_BAD_ALIGN;
+    if ((a.epi == MX_EPI_STORE_F32 || a.epi == MX_EPI_STORE_BF16 || a.epi == MX_EPI_ATOMIC_F32) && (((uintptr_t)a.out & 15) || (a.out_ld & 7))) return ERR_BAD_ALIGN;
     if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
     const int NW = a.dual ? 2 * a.rows_a : a.rows_a;
     const int n_atoms = 1 + (NW + 127) / 128;
@@ -534,6 +578,12 @@ int mx_device_error(int* out, cudaStream_t stream) {
 int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream) {
     if (!x || !q8 || !sf || rows < 0 || K <= 0 || K % 32) return ERR_BAD_ARG;
     if (rows == 0) return 0;
+    if (!((uintptr_t)x & 15) && x_ld % 8 == 0 && !((uintptr_t)q8 & 7)) {
+        const long threads = (long)rows * (K / 8);
+        mx_quantize_rows_vec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf);
+        B200_CHECK_LAUNCH();
+        return 0;
+    }
     const long warps = (long)rows * (K / 32);
     mx_quantize_rows_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf);
     B200_CHECK_LAUNCH();
