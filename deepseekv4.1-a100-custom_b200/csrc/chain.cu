@@ -13,6 +13,7 @@ namespace b200 {
 constexpr int ROUTE_THREADS = 128;
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
+constexpr int MX_AUTO_MIN_TOKENS = 8;   // automatic engine choice: up to this many tokens the weight-streaming kernels are faster (measured)
 constexpr int MX_ND_DECODE = 32;        // tokens per work of the block-scaled tensor-core path
 
 struct RouteArgs {
@@ -393,11 +394,11 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     const bool small = P <= ROUTE_MAX_PAIRS;
     // engine: 1 = weight streaming with in-register dequantisation (any scale format, decode-sized batches only),
     //         2 = block-scaled tensor cores (E8M0 scales, natural k order of the shared expert), 0 = automatic:
-    //         streaming for decode-sized batches (<= 64 tokens), tensor cores beyond
+    //         streaming for the smallest batches (<= MX_AUTO_MIN_TOKENS tokens), tensor cores beyond
     const bool mx_ok = m->expert_fmt == SK_FMT_FP4_E8M0 && (!m->has_shared || (m->shared_fmt == SK_FMT_FP8_E8M0 && !m->sh_permk));
     if ((m->engine == 2 || !small) && !mx_ok) return ERR_UNSUPPORTED;
     if (m->engine == 1 && !small) return ERR_UNSUPPORTED;
-    const bool use_mx = m->engine == 2 || !small || (m->engine == 0 && mx_ok && T > 64);
+    const bool use_mx = m->engine == 2 || !small || (m->engine == 0 && mx_ok && T > MX_AUTO_MIN_TOKENS);
     const bool shared = m->has_shared && m->out;
     cudaError_t ce;
     int rc;

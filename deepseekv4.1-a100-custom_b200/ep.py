@@ -58,16 +58,8 @@ class EPMoE:
         return self.layer.forward(x_all, logits_all, final=False, want_routed=True)
 
     def _shared_cuda(self, x_local, routed_local):
-        from .fused import fake_quant_fp8, swiglu_quant
         from .fused2 import moe_combine
-        from .w8 import linear_w
-        L = self.layer
-        ys = None
-        if L.sh_w13 is not None:
-            xq = fake_quant_fp8(x_local, 32)
-            hs = swiglu_quant(linear_w(xq, L.sh_w13), None, L.inter, L.swiglu_limit)
-            ys = linear_w(hs, L.sh_w2)
-        return moe_combine(routed_local.unsqueeze(1), ys)
+        return moe_combine(routed_local.unsqueeze(1), self.layer.shared_expert(x_local))
 
     # ---- the exchange
     def forward(self, x_local: torch.Tensor, logits_local: torch.Tensor, counts: list[int] | None = None) -> torch.Tensor:

@@ -35,7 +35,7 @@ class MoELayer:
         self.topk, self.gate_bias, self.gate_temp, self.route_scale = topk, gate_bias, gate_temp, route_scale
         self.score_func, self.norm, self.swiglu_limit = score_func, norm_topk_prob and topk > 1, swiglu_limit
         self.device = dev
-        # engine 0 = automatic (weight streaming up to 64 tokens, block-scaled tensor cores beyond), 1 = weight streaming with
+        # engine 0 = automatic (weight streaming up to 8 tokens, block-scaled tensor cores beyond), 1 = weight streaming with
         # in-register dequantisation, 2 = block-scaled tensor cores.  The tensor-core path reads the shared expert in natural k
         # order, so a natural-order copy is kept next to the W8 container.
         self.engine = engine
@@ -48,7 +48,33 @@ class MoELayer:
             self._sh_nat = (unpermute_k(sh_w13.w8), unpermute_k(sh_w2.w8))
 
     def _use_mx(self, tokens: int) -> bool:
-        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 64)
+        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 8)
+
+    def shared_expert(self, x: torch.Tensor) -> torch.Tensor | None:
+        """The shared expert alone: x bf16 [T, D] -> ys bf16 [T, D] (None without one); the values of dsv41/model.py:1635-1638 on FP8
+        fake-quantised activations.  Tensor-core kernels when the layer would use them for T tokens, else the streaming ones."""
+        if self.sh_w13 is None:
+            return None
+        T = x.shape[0]
+        if self._use_mx(T) and self._sh_nat is not None:
+            from . import cukern
+            w13n, w2n = self._sh_nat
+            tpw = 128 if T > 64 else 32
+            works = (T + tpw - 1) // tpw
+            rows1 = 128
+            while rows1 > 32 and works * (self.inter // rows1) < 148:
+                rows1 //= 2
+            rows2 = 256
+            while rows2 > 32 and works * (self.dim // rows2) < 148:
+                rows2 //= 2
+            q8, sf = cukern.mx_quantize_rows(x)
+            h8, hsf = cukern.mx_grouped(w13n, self.sh_w13.s8, q8, sf, None, None, None, None, None, T, epilogue="swiglu_q8", limit=self.swiglu_limit,
+                                        round_gu_bf16=True, tokens_per_work=tpw, rows_per_tile=rows1)
+            return cukern.mx_grouped(w2n, self.sh_w2.s8, h8, hsf, None, None, None, None, None, T, epilogue="bf16", tokens_per_work=tpw, rows_per_tile=rows2)
+        from .fused import fake_quant_fp8, swiglu_quant
+        from .w8 import linear_w
+        hs = swiglu_quant(linear_w(fake_quant_fp8(x, 32), self.sh_w13), None, self.inter, self.swiglu_limit)
+        return linear_w(hs, self.sh_w2)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, *, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
                 x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, prof_events=None):
