@@ -364,17 +364,19 @@ def run_gpu(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.workload, world), "clocks": clocks,
             "e2e": {"value": S / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
-            "gpu_launches": ((11 if S > 64 else (8 if layer._use_mx(S) else 6)) + (0 if world == 1 else 3)) * args.steps}
+            "gpu_launches": ((9 if S > 64 else 6) + (0 if world == 1 else 3)) * args.steps}
     if world == 1:
         durs = [prof[args.warmup + i][0].elapsed_time(prof[args.warmup + i][1]) for i in range(args.steps)]
         u_steps = [uniq[(args.warmup + i) % NP] for i in range(args.steps)]
         avg_ms = statistics.mean(durs)
         layer_bytes = statistics.mean(u_steps) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
         if S <= 64:
-            alg = statistics.mean(u_steps) * exp_b13
+            mx = layer._use_mx(S)
+            # the tensor-core launch streams the shared expert's gate/up matrix (FP8 + 32x32 scales) in the same kernel
+            alg = statistics.mean(u_steps) * exp_b13 + ((2 * I * D + 2 * I * D // 1024) if mx else 0)
             achieved = alg / (avg_ms * 1e-3) / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                                "kernel": ("mx_gemm_kernel (routed gate/up weight stream on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)" if layer._use_mx(S)
+                                "kernel": ("mx_gemm_kernel (gate/up weight stream of the routed experts and the shared expert on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)" if mx
                                            else "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"),
                                 "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
                                 "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": statistics.mean(u_steps),
@@ -382,14 +384,14 @@ def run_gpu(args):
                                                 "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak}}
         else:
             tpeak, tsrc = measured_tensor_peak()
-            flops1 = S * TOPK * 2.0 * D * 2 * I          # routed gate/up grouped GEMM (the timed kernel)
-            flops_layer = S * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)
+            flops1 = S * (TOPK + 1) * 2.0 * D * 2 * I    # gate/up GEMM of the routed experts and the shared expert (the timed kernel)
+            flops_layer = S * (TOPK + 1) * (2.0 * D * 2 * I + 2.0 * I * D)
             achieved = flops1 / (avg_ms * 1e-3) / 1e12
             line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak, "traffic": None,
-                                "kernel": "mx_gemm_kernel (routed gate/up grouped GEMM, tcgen05 kind::mxf8f6f4 block-scaled, + SwiGLU + FP8 quant)",
+                                "kernel": "mx_gemm_kernel (gate/up grouped GEMM of routed + shared experts, tcgen05 kind::mxf8f6f4 block-scaled, + SwiGLU + FP8 quant)",
                                 "algorithmic_flops_per_launch": flops1, "avg_launch_ms": avg_ms, "peak_source": tsrc,
                                 "unique_experts_per_step": statistics.mean(u_steps),
-                                "whole_layer": {"routed_flops_per_step": flops_layer, "achieved_tflops": flops_layer / (ms * 1e-3) / 1e12,
+                                "whole_layer": {"flops_per_step": flops_layer, "achieved_tflops": flops_layer / (ms * 1e-3) / 1e12,
                                                 "frac": flops_layer / (ms * 1e-3) / 1e12 / tpeak, "weight_bytes_per_step": layer_bytes,
                                                 "weight_stream_floor_ms": layer_bytes / (peak * 1e9) * 1e3}}
         # other decode batch sizes of the same configuration (short runs, same method)
@@ -412,8 +414,8 @@ def run_gpu(args):
                 sweep[name] = {"tokens_per_s": s2 / (m2 * 1e-3), "ms_per_step": m2, "unique_experts": statistics.mean(u2), "layer_gbs": b2 / (m2 * 1e-3) / 1e9,
                                "layer_hbm_frac": b2 / (m2 * 1e-3) / 1e9 / peak}
                 if s2 > 64:
-                    f2 = s2 * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)
-                    sweep[name]["routed_tflops"] = f2 / (m2 * 1e-3) / 1e12
+                    f2 = s2 * (TOPK + 1) * (2.0 * D * 2 * I + 2.0 * I * D)
+                    sweep[name]["tflops"] = f2 / (m2 * 1e-3) / 1e12
                     sweep[name]["frac_of_bf16_peak"] = f2 / (m2 * 1e-3) / 1e12 / measured_tensor_peak()[0]
                 del xs2, ls2, o2
         line["sweep"] = sweep

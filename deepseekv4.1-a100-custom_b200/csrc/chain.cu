@@ -13,7 +13,7 @@ namespace b200 {
 constexpr int ROUTE_THREADS = 128;
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
-constexpr int MX_AUTO_MIN_TOKENS = 8;   // automatic engine choice: up to this many tokens the weight-streaming kernels are faster (measured)
+constexpr int MX_AUTO_MIN_TOKENS = 4;   // automatic engine choice: up to this many tokens the weight-streaming kernels are faster (measured)
 constexpr int MX_ND_DECODE = 32;        // tokens per work of the block-scaled tensor-core path
 
 struct RouteArgs {
@@ -438,47 +438,51 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         // weight rows per tile: as many as the tensor-core instruction takes (256) once there are enough (work, tile) items to
         // balance over the SMs; fewer rows per tile for the smallest batches
         const int rows1 = P >= 48 ? 128 : (P >= 24 ? 64 : 32), rows2 = 2 * rows1;
+        // each GEMM launch carries the routed experts (problem 0) and, behind them in the same item list, the shared expert
+        // (problem 1: one FP8 matrix against all tokens)
         MxArgs g1{};
-        g1.w = m->w13; g1.w_estride = (long long)2 * I * (D / 2); g1.n_experts = shard_n; g1.a_fmt = MX_A_E2M1;
-        g1.s = (const uint8_t*)m->s13; g1.s_estride = (long long)2 * I * (D / 32); g1.s_rstride = D / 32; g1.s_row_shift = 0;
-        g1.N = 2 * I; g1.K = D; g1.x8 = w.x8s; g1.x8_rows = P + 128; g1.xsf = w.xsfs; g1.xsf_ld = D / 32;
-        g1.work = w.work; g1.n_work = w.n_work; g1.nd = nd; g1.rows_a = rows1; g1.dual = 1; g1.kb = 4; g1.epi = MX_EPI_SWIGLU_Q8;
-        g1.pair_w = w.pair_w; g1.out = w.hq8; g1.out_ld = I; g1.out_sf = w.hsf; g1.out_sf_ld = I / 32; g1.limit = m->swiglu_limit; g1.inter = I;
+        g1.n_prob = shared ? 2 : 1;
+        g1.K = D; g1.nd = nd; g1.rows_a = rows1; g1.dual = 1; g1.kb = 4; g1.limit = m->swiglu_limit; g1.inter = I;
+        {
+            MxProb& q = g1.p[0];
+            q.w = m->w13; q.w_estride = (long long)2 * I * (D / 2); q.n_experts = shard_n; q.a_fmt = MX_A_E2M1;
+            q.s = (const uint8_t*)m->s13; q.s_estride = (long long)2 * I * (D / 32); q.s_rstride = D / 32; q.s_row_shift = 0;
+            q.N = 2 * I; q.x8 = w.x8s; q.x8_rows = P + 128; q.xsf = w.xsfs; q.xsf_ld = D / 32;
+            q.work = w.work; q.n_work = w.n_work; q.epi = MX_EPI_SWIGLU_Q8;
+            q.pair_w = w.pair_w; q.out = w.hq8; q.out_ld = I; q.out_sf = w.hsf; q.out_sf_ld = I / 32;
+        }
+        if (shared) {
+            MxProb& q = g1.p[1];
+            q.w = m->sh_w13; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
+            q.s = (const uint8_t*)m->sh_s13; q.s_rstride = m->sh_s13_cols; q.s_row_shift = 5;
+            q.N = 2 * I; q.x8 = w.x8t; q.x8_rows = T + 128; q.xsf = w.xsft; q.xsf_ld = D / 32;
+            q.work = nullptr; q.dense_rows = T; q.n_work_host = (T + nd - 1) / nd; q.epi = MX_EPI_SWIGLU_Q8;
+            q.out = w.hs8; q.out_ld = I; q.out_sf = w.hssf; q.out_sf_ld = I / 32; q.round_gu_bf16 = 1;
+        }
         if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
         if ((rc = mx_launch(g1, stream))) return rc;
         if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
         MxArgs g2{};
-        g2.w = m->w2; g2.w_estride = (long long)D * (I / 2); g2.n_experts = shard_n; g2.a_fmt = MX_A_E2M1;
-        g2.s = (const uint8_t*)m->s2; g2.s_estride = (long long)D * (I / 32); g2.s_rstride = I / 32; g2.s_row_shift = 0;
-        g2.N = D; g2.K = I; g2.x8 = w.hq8; g2.x8_rows = P + 128; g2.xsf = w.hsf; g2.xsf_ld = I / 32;
-        g2.work = w.work; g2.n_work = w.n_work; g2.nd = nd; g2.rows_a = rows2; g2.dual = 0; g2.kb = 4;
-        g2.epi = small ? MX_EPI_STORE_F32 : MX_EPI_ATOMIC_F32;
-        g2.pair_out = w.pair_out; g2.out = small ? w.y2 : w.acc; g2.out_ld = D;
-        if ((rc = mx_launch(g2, stream))) return rc;
-        if (shared) {
-            // one matrix, few works: tiles small enough that (works x tiles) still covers the SMs
-            const int works_s = (T + nd - 1) / nd;
-            int rows1s = 128;
-            while (rows1s > 32 && (long)works_s * (I / rows1s) < 148) rows1s >>= 1;
-            int rows2s = 256;
-            while (rows2s > 32 && (long)works_s * (D / rows2s) < 148) rows2s >>= 1;
-            MxArgs s1{};
-            s1.w = m->sh_w13; s1.n_experts = 1; s1.a_fmt = MX_A_E4M3;
-            s1.s = (const uint8_t*)m->sh_s13; s1.s_rstride = m->sh_s13_cols; s1.s_row_shift = 5;
-            s1.N = 2 * I; s1.K = D; s1.x8 = w.x8t; s1.x8_rows = T + 128; s1.xsf = w.xsft; s1.xsf_ld = D / 32;
-            s1.work = nullptr; s1.dense_rows = T; s1.n_work_host = (T + nd - 1) / nd;
-            s1.nd = nd; s1.rows_a = rows1s; s1.dual = 1; s1.kb = 4; s1.epi = MX_EPI_SWIGLU_Q8;
-            s1.out = w.hs8; s1.out_ld = I; s1.out_sf = w.hssf; s1.out_sf_ld = I / 32; s1.limit = m->swiglu_limit; s1.inter = I; s1.round_gu_bf16 = 1;
-            if ((rc = mx_launch(s1, stream))) return rc;
-            MxArgs s2{};
-            s2.w = m->sh_w2; s2.n_experts = 1; s2.a_fmt = MX_A_E4M3;
-            s2.s = (const uint8_t*)m->sh_s2; s2.s_rstride = m->sh_s2_cols; s2.s_row_shift = 5;
-            s2.N = D; s2.K = I; s2.x8 = w.hs8; s2.x8_rows = T + 128; s2.xsf = w.hssf; s2.xsf_ld = I / 32;
-            s2.work = nullptr; s2.dense_rows = T; s2.n_work_host = (T + nd - 1) / nd;
-            s2.nd = nd; s2.rows_a = rows2s; s2.dual = 0; s2.kb = 4; s2.epi = MX_EPI_STORE_BF16;
-            s2.out = w.ys; s2.out_ld = D;
-            if ((rc = mx_launch(s2, stream))) return rc;
+        g2.n_prob = shared ? 2 : 1;
+        g2.K = I; g2.nd = nd; g2.rows_a = rows2; g2.dual = 0; g2.kb = 4;
+        {
+            MxProb& q = g2.p[0];
+            q.w = m->w2; q.w_estride = (long long)D * (I / 2); q.n_experts = shard_n; q.a_fmt = MX_A_E2M1;
+            q.s = (const uint8_t*)m->s2; q.s_estride = (long long)D * (I / 32); q.s_rstride = I / 32; q.s_row_shift = 0;
+            q.N = D; q.x8 = w.hq8; q.x8_rows = P + 128; q.xsf = w.hsf; q.xsf_ld = I / 32;
+            q.work = w.work; q.n_work = w.n_work;
+            q.epi = small ? MX_EPI_STORE_F32 : MX_EPI_ATOMIC_F32;
+            q.pair_out = w.pair_out; q.out = small ? w.y2 : w.acc; q.out_ld = D;
         }
+        if (shared) {
+            MxProb& q = g2.p[1];
+            q.w = m->sh_w2; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
+            q.s = (const uint8_t*)m->sh_s2; q.s_rstride = m->sh_s2_cols; q.s_row_shift = 5;
+            q.N = D; q.x8 = w.hs8; q.x8_rows = T + 128; q.xsf = w.hssf; q.xsf_ld = I / 32;
+            q.work = nullptr; q.dense_rows = T; q.n_work_host = (T + nd - 1) / nd; q.epi = MX_EPI_STORE_BF16;
+            q.out = w.ys; q.out_ld = D;
+        }
+        if ((rc = mx_launch(g2, stream))) return rc;
     } else {
         const __nv_bfloat16* xin = m->x_is_quantized ? (const __nv_bfloat16*)m->x : w.xq;
         const int sbytes = m->expert_fmt == SK_FMT_FP4_BF16S ? 2 : 1;
@@ -560,13 +564,15 @@ extern "C" int b200_mx_grouped_gemm(const void* w, long long w_estride, const vo
     if (fmt != SK_FMT_FP4_E8M0 && fmt != SK_FMT_FP8_E8M0) return ERR_UNSUPPORTED;
     if (n_rows == 0) return 0;
     MxArgs a{};
-    a.w = w; a.w_estride = w_estride; a.n_experts = n_local_experts; a.a_fmt = fmt == SK_FMT_FP4_E8M0 ? MX_A_E2M1 : MX_A_E4M3;
-    a.s = (const uint8_t*)s; a.s_estride = s_estride;
-    a.s_rstride = fmt == SK_FMT_FP4_E8M0 ? K / 32 : s_cols; a.s_row_shift = fmt == SK_FMT_FP4_E8M0 ? 0 : 5;
-    a.N = N; a.K = K; a.x8 = (const uint8_t*)x8; a.x8_rows = x8_rows; a.xsf = (const uint8_t*)xsf; a.xsf_ld = K / 32;
+    MxProb& q = a.p[0];
+    a.n_prob = 1;
+    q.w = w; q.w_estride = w_estride; q.n_experts = n_local_experts; q.a_fmt = fmt == SK_FMT_FP4_E8M0 ? MX_A_E2M1 : MX_A_E4M3;
+    q.s = (const uint8_t*)s; q.s_estride = s_estride;
+    q.s_rstride = fmt == SK_FMT_FP4_E8M0 ? K / 32 : s_cols; q.s_row_shift = fmt == SK_FMT_FP4_E8M0 ? 0 : 5;
+    q.N = N; a.K = K; q.x8 = (const uint8_t*)x8; q.x8_rows = x8_rows; q.xsf = (const uint8_t*)xsf; q.xsf_ld = K / 32;
     a.nd = tokens_per_work; a.rows_a = rows_per_tile; a.kb = 4;
-    a.epi = epilogue; a.dual = epilogue == MX_EPI_SWIGLU_Q8; a.inter = a.dual ? N / 2 : 0; a.limit = limit; a.round_gu_bf16 = round_gu_bf16;
-    a.pair_out = pair_out; a.pair_w = pair_w; a.out = out; a.out_ld = out_ld; a.out_sf = (uint8_t*)out_sf; a.out_sf_ld = a.dual ? N / 2 / 32 : 0;
+    q.epi = epilogue; a.dual = epilogue == MX_EPI_SWIGLU_Q8; a.inter = a.dual ? N / 2 : 0; a.limit = limit; q.round_gu_bf16 = round_gu_bf16;
+    q.pair_out = pair_out; q.pair_w = pair_w; q.out = out; q.out_ld = out_ld; q.out_sf = (uint8_t*)out_sf; q.out_sf_ld = a.dual ? N / 2 / 32 : 0;
     if (grp_expert && n_groups > 0) {
         if (!grp_start || !workspace || workspace_bytes < b200_mx_grouped_workspace_bytes(n_rows) || ((uintptr_t)workspace & 15)) return ERR_WORKSPACE;
         Carver cv{(char*)workspace, workspace_bytes};
@@ -576,9 +582,9 @@ extern "C" int b200_mx_grouped_gemm(const void* w, long long w_estride, const vo
         if (shard_n > n_local_experts) shard_n = n_local_experts;
         int rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_rows, shard_start, shard_n, work, n_work, n_rows, stream, tokens_per_work);
         if (rc) return rc;
-        a.work = work; a.n_work = n_work;
+        q.work = work; q.n_work = n_work;
     } else {
-        a.work = nullptr; a.dense_rows = n_rows; a.n_work_host = (n_rows + tokens_per_work - 1) / tokens_per_work;
+        q.work = nullptr; q.dense_rows = n_rows; q.n_work_host = (n_rows + tokens_per_work - 1) / tokens_per_work;
     }
     return mx_launch(a, stream);
 }

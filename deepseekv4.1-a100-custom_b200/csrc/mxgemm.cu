@@ -94,8 +94,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
 // instruction should carry as many weight bytes as possible).  D[token, weight row] lives in TMEM columns [0, N_w).
 //   dual (SwiGLU epilogue): N_w = 2 * rows_w, columns [0, rows_w) = gate rows row0.., columns [rows_w, 2 rows_w) = up rows
 //   single:                 N_w = rows_w consecutive rows
-__global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, const __grid_constant__ CUtensorMap tm_w,
-                                                                 const __grid_constant__ CUtensorMap tm_x) {
+// One launch runs up to two problems that share K, the tile shape and the token count per work (the routed experts and the
+// shared expert of one layer step): the (work, tile) items of problem 0 are followed by those of problem 1 in one flat list that
+// is cut evenly over the CTAs, so the small second problem fills the tail of the first.
+__global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, const __grid_constant__ CUtensorMap tm_w0,
+                                                                 const __grid_constant__ CUtensorMap tm_x0, const __grid_constant__ CUtensorMap tm_w1,
+                                                                 const __grid_constant__ CUtensorMap tm_x1) {
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long bars[3 * MX_MAX_STAGES + 4];  // full_ab[s], full_sf[s], empty[s], acc_full[2], acc_empty[2]
     __shared__ uint32_t tmem_base_sh;
@@ -121,10 +125,12 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
 
     const int kblocks = a.K >> 7;                       // 128-wide k blocks
     const int spi = (kblocks + KB - 1) / KB;            // stages per item
-    const int n_rows_out = a.dual ? a.inter : a.N;
-    const int ipw = (n_rows_out + rows_w - 1) / rows_w; // items per work
-    const int n_work = a.n_work ? *a.n_work : a.n_work_host;
-    const long total = (long)n_work * ipw;
+    // items per work and items in all of each problem
+    const int ipw0 = ((a.dual ? a.inter : a.p[0].N) + rows_w - 1) / rows_w;
+    const int ipw1 = a.n_prob > 1 ? ((a.dual ? a.inter : a.p[1].N) + rows_w - 1) / rows_w : 1;
+    const long items0 = (long)(a.p[0].n_work ? *a.p[0].n_work : a.p[0].n_work_host) * ipw0;
+    const long items1 = a.n_prob > 1 ? (long)(a.p[1].n_work ? *a.p[1].n_work : a.p[1].n_work_host) * ipw1 : 0;
+    const long total = items0 + items1;
     const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
     const int n_acc = (2 * NW <= MX_ACC_COLS_MAX) ? 2 : 1;  // two accumulator buffers (epilogue overlaps the next item) when they fit
     const uint32_t sf_col0 = (uint32_t)(n_acc * NW);        // the scale columns follow the accumulators
@@ -151,46 +157,69 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sh;
 
-    auto get_work = [&](int wk) -> int4 {
-        if (a.work) return __ldg(a.work + wk);
-        const int rem = a.dense_rows - wk * nd;
+    // position in the flat item list: problem, work, tile of the work; `w` = {local expert, first token row, tokens, -}
+    struct ItemCur { long item; int pr, wk, it; int4 w; };
+    auto get_work = [&](int pr, int wk) -> int4 {
+        const MxProb& P = a.p[pr];
+        if (P.work) return __ldg(P.work + wk);
+        const int rem = P.dense_rows - wk * nd;
         return make_int4(0, wk * nd, rem < nd ? rem : nd, 0);
     };
-    const int wk_lo = (int)(lo / ipw), it_lo = (int)(lo - (long)wk_lo * ipw);
-    const uint32_t w_tx = a.a_fmt == MX_A_E2M1 ? w_tile / 2 : w_tile;  // packed FP4 boxes count the bytes actually written
+    auto locate = [&](long item, bool fetch) -> ItemCur {
+        ItemCur c;
+        c.item = item;
+        c.pr = item >= items0 ? 1 : 0;
+        const long rel = c.pr ? item - items0 : item;
+        const int ipw = c.pr ? ipw1 : ipw0;
+        c.wk = (int)(rel / ipw);
+        c.it = (int)(rel - (long)c.wk * ipw);
+        c.w = (fetch && item < total) ? get_work(c.pr, c.wk) : make_int4(0, 0, 0, 0);
+        return c;
+    };
+    auto next_item = [&](ItemCur& c, bool fetch) {
+        ++c.item;
+        if (c.item >= hi) return;
+        if (c.pr == 0 && c.item == items0) {
+            c.pr = 1; c.wk = 0; c.it = 0;
+            if (fetch) c.w = get_work(1, 0);
+            return;
+        }
+        if (++c.it == (c.pr ? ipw1 : ipw0)) {
+            c.it = 0;
+            ++c.wk;
+            if (fetch) c.w = get_work(c.pr, c.wk);
+        }
+    };
 
     if (lo < hi) {
         if (warp == 0) {
             // ------------------------------------------------ TMA producer (one thread)
             if (lane == 0) {
-                tma_prefetch_desc(&tm_w);
-                tma_prefetch_desc(&tm_x);
-                // flat sequence of stages (item, k range)
-                struct PCur { long item; int wk, it, st; int4 w; };
-                auto advance = [&](PCur& c) {
-                    if (++c.st < spi) return;
-                    c.st = 0;
-                    ++c.item;
-                    if (++c.it == ipw) { c.it = 0; ++c.wk; if (c.item < hi) c.w = get_work(c.wk); }
-                };
-                PCur cur{lo, wk_lo, it_lo, 0, get_work(wk_lo)};
+                tma_prefetch_desc(&tm_w0);
+                tma_prefetch_desc(&tm_x0);
+                if (a.n_prob > 1) { tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_x1); }
+                ItemCur c = locate(lo, true);
                 uint32_t n = 0;
-                for (; cur.item < hi && !abort_flag; ++n) {
-                    const int4 w = cur.w;
-                    const int row0 = cur.it * rows_w, st = cur.st;
-                    const uint32_t s = n % NS, ph = (n / NS) & 1;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 11)) break;
-                    const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
-                    mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * (x_box + w_tx));
-                    const uint32_t dst = smem_u32(ring + (size_t)s * stage_bytes);
-                    for (int b = 0; b < nkb; ++b) {
-                        const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
-                        const uint32_t wdst = dst + (uint32_t)KB * x_box + (uint32_t)b * w_tile;
-                        tma_load_3d(wdst, &tm_w, kx, row0, w.x, bar_full_ab(s));
-                        if (a.dual) tma_load_3d(wdst + w_half, &tm_w, kx, a.inter + row0, w.x, bar_full_ab(s));
-                        tma_load_2d(dst + (uint32_t)b * x_box, &tm_x, kx, w.y, bar_full_ab(s));
+                for (; c.item < hi && !abort_flag; next_item(c, true)) {
+                    const CUtensorMap* tw = c.pr ? &tm_w1 : &tm_w0;
+                    const CUtensorMap* tx = c.pr ? &tm_x1 : &tm_x0;
+                    // packed FP4 boxes count the bytes actually written
+                    const uint32_t w_tx = a.p[c.pr].a_fmt == MX_A_E2M1 ? w_tile / 2 : w_tile;
+                    const int row0 = c.it * rows_w;
+                    for (int st = 0; st < spi; ++st, ++n) {
+                        const uint32_t s = n % NS, ph = (n / NS) & 1;
+                        if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 11)) break;
+                        const int kb0 = st * KB, nkb = min(KB, kblocks - kb0);
+                        mbar_expect_tx(bar_full_ab(s), (uint32_t)nkb * (x_box + w_tx));
+                        const uint32_t dst = smem_u32(ring + (size_t)s * stage_bytes);
+                        for (int b = 0; b < nkb; ++b) {
+                            const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
+                            const uint32_t wdst = dst + (uint32_t)KB * x_box + (uint32_t)b * w_tile;
+                            tma_load_3d(wdst, tw, kx, row0, c.w.x, bar_full_ab(s));
+                            if (a.dual) tma_load_3d(wdst + w_half, tw, kx, a.inter + row0, c.w.x, bar_full_ab(s));
+                            tma_load_2d(dst + (uint32_t)b * x_box, tx, kx, c.w.y, bar_full_ab(s));
+                        }
                     }
-                    advance(cur);
                 }
                 // every load issued above must have landed before the CTA may exit
                 for (int k = 0; k < NS && k < (int)n; ++k) {
@@ -202,11 +231,11 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 }
             }
         } else if (warp == 1) {
-            // ------------------------------------------------ MMA issuer (one thread)
+            // ------------------------------------------------ MMA issuer (one thread): scale atoms -> TMEM (tcgen05.cp), then the MMAs
             if (lane == 0) {
                 uint32_t n = 0, acc_it = 0;
-                const int b_fmt = a.a_fmt;  // weight format (the B operand); the tokens (A operand) are e4m3
                 for (long item = lo; item < hi && !abort_flag; ++item, ++acc_it) {
+                    const int b_fmt = a.p[item >= items0 ? 1 : 0].a_fmt;  // weight format (the B operand); the tokens (A operand) are e4m3
                     const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
                     if (!mbar_wait(bar_acc_empty(buf), aph ^ 1, &abort_flag, &g_mx_error, 21)) break;
                     tc_fence_after();
@@ -243,56 +272,57 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
             const int r = tid - 256;
             const uint32_t atom_off = (uint32_t)(r & 31) * 16u + (uint32_t)(r >> 5) * 4u;
             struct Cur {
-                long item; int wk, it, st; int4 w;
+                ItemCur c; int st;
                 const uint8_t *s_0, *s_1, *s_x; bool brow, w0, w1;
             };
-            auto wrow = [&](int row0, int c) -> int {  // weight row of tile column c
-                if (a.dual) return c < rows_w ? row0 + c : a.inter + row0 + (c - rows_w);
-                return row0 + c;
+            auto wrow = [&](int row0, int col) -> int {  // weight row of tile column col
+                if (a.dual) return col < rows_w ? row0 + col : a.inter + row0 + (col - rows_w);
+                return row0 + col;
             };
-            auto setup = [&](Cur& c) {
-                const int row0 = c.it * rows_w;
-                const uint8_t* sbase = a.s + (long long)c.w.x * a.s_estride;
-                c.w0 = r < NW;
-                c.w1 = r + 128 < NW;
-                const int ra = min(wrow(row0, c.w0 ? r : 0), a.N - 1), rb = min(wrow(row0, c.w1 ? r + 128 : 0), a.N - 1);
-                c.s_0 = sbase + (long)(ra >> a.s_row_shift) * a.s_rstride;
-                c.s_1 = sbase + (long)(rb >> a.s_row_shift) * a.s_rstride;
-                c.brow = r < c.w.z;
-                c.s_x = a.xsf + (long)(c.w.y + (c.brow ? r : 0)) * a.xsf_ld;
+            auto setup = [&](Cur& u) {
+                const MxProb& P = a.p[u.c.pr];
+                const int row0 = u.c.it * rows_w;
+                const uint8_t* sbase = P.s + (long long)u.c.w.x * P.s_estride;
+                u.w0 = r < NW;
+                u.w1 = r + 128 < NW;
+                const int ra = min(wrow(row0, u.w0 ? r : 0), P.N - 1), rb = min(wrow(row0, u.w1 ? r + 128 : 0), P.N - 1);
+                u.s_0 = sbase + (long)(ra >> P.s_row_shift) * P.s_rstride;
+                u.s_1 = sbase + (long)(rb >> P.s_row_shift) * P.s_rstride;
+                u.brow = r < u.c.w.z;
+                u.s_x = P.xsf + (long)(u.c.w.y + (u.brow ? r : 0)) * P.xsf_ld;
             };
-            auto advance = [&](Cur& c) {
-                if (++c.st < spi) return;
-                c.st = 0;
-                ++c.item;
-                if (++c.it == ipw) { c.it = 0; ++c.wk; if (c.item < hi) c.w = get_work(c.wk); }
-                if (c.item < hi) setup(c);
+            auto advance = [&](Cur& u) {
+                if (++u.st < spi) return;
+                u.st = 0;
+                next_item(u.c, true);
+                if (u.c.item < hi) setup(u);
             };
             constexpr int PD = 3;
             uint32_t q[PD][3][4];
-            auto load = [&](const Cur& c, uint32_t (&v)[3][4]) {
-                if (c.item >= hi) return;
-                const int kb0 = c.st * KB, nkb = min(KB, kblocks - kb0);
+            auto load = [&](const Cur& u, uint32_t (&v)[3][4]) {
+                if (u.c.item >= hi) return;
+                const int kb0 = u.st * KB, nkb = min(KB, kblocks - kb0);
 #pragma unroll
                 for (int b = 0; b < 4; ++b) {
                     if (b >= nkb) break;
                     const int g0 = (kb0 + b) * 4;  // first 32-k group of the k block
-                    v[0][b] = c.brow ? ldg_stream4(c.s_x + g0) : 0x7F7F7F7Fu;
-                    v[1][b] = c.w0 ? ldg_stream4(c.s_0 + g0) : 0x7F7F7F7Fu;
-                    v[2][b] = c.w1 ? ldg_stream4(c.s_1 + g0) : 0x7F7F7F7Fu;
+                    v[0][b] = u.brow ? ldg_stream4(u.s_x + g0) : 0x7F7F7F7Fu;
+                    v[1][b] = u.w0 ? ldg_stream4(u.s_0 + g0) : 0x7F7F7F7Fu;
+                    v[2][b] = u.w1 ? ldg_stream4(u.s_1 + g0) : 0x7F7F7F7Fu;
                 }
             };
             Cur use;
-            use.item = lo; use.wk = wk_lo; use.it = it_lo; use.st = 0; use.w = get_work(wk_lo);
+            use.c = locate(lo, true);
+            use.st = 0;
             setup(use);
             Cur ld = use;
 #pragma unroll
             for (int i = 0; i < PD; ++i) { load(ld, q[i]); advance(ld); }
             uint32_t n = 0;
-            while (use.item < hi && !abort_flag) {
+            while (use.c.item < hi && !abort_flag) {
 #pragma unroll
                 for (int i = 0; i < PD; ++i) {
-                    if (use.item >= hi) break;
+                    if (use.c.item >= hi) break;
                     const uint32_t s = n % NS, ph = (n / NS) & 1;
                     const int kb0 = use.st * KB, nkb = min(KB, kblocks - kb0);
                     if (!mbar_wait(bar_empty(s), ph ^ 1, &abort_flag, &g_mx_error, 31)) break;
@@ -318,22 +348,23 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
             // 32 q .. 32 q + 31 = tokens; the two groups split the weight-row columns.  A thread owns one token.
             const int q = warp & 3, egrp = warp >= 12 ? 1 : 0;
             const int t = q * 32 + lane;
-            int wk = wk_lo, it = it_lo;
-            int4 w = get_work(wk);
+            ItemCur c = locate(lo, true);
             uint32_t acc_it = 0;
-            for (long item = lo; item < hi && !abort_flag; ++item, ++acc_it) {
+            for (; c.item < hi && !abort_flag; next_item(c, true), ++acc_it) {
+                const MxProb& P = a.p[c.pr];
+                const int4 w = c.w;
                 const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
                 const bool ready = mbar_wait(bar_acc_full(buf), aph, &abort_flag, &g_mx_error, 41);
                 tc_fence_after();
-                const int row0 = it * rows_w;
+                const int row0 = c.it * rows_w;
                 const bool warp_on = ready && q * 32 < w.z;  // warp-uniform: some token of this warp exists
                 const bool tok_on = t < w.z;
                 const int prow = w.y + (tok_on ? t : 0);
-                const float pw = (a.pair_w && tok_on) ? __ldg(a.pair_w + prow) : 1.f;
-                const long orow = (a.pair_out && tok_on) ? (long)__ldg(a.pair_out + prow) : (long)prow;
+                const float pw = (P.pair_w && tok_on) ? __ldg(P.pair_w + prow) : 1.f;
+                const long orow = (P.pair_out && tok_on) ? (long)__ldg(P.pair_out + prow) : (long)prow;
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
                 if (warp_on) {
-                    if (a.epi == MX_EPI_SWIGLU_Q8) {
+                    if (P.epi == MX_EPI_SWIGLU_Q8) {
                         // columns c = SwiGLU column row0 + c; 32 consecutive columns are one quantisation group (dsv41/fused.py:285-306)
                         for (int c0 = egrp * 32; c0 < rows_w; c0 += 64) {
                             uint32_t g[32], u[32];
@@ -345,30 +376,30 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                             if (!tok_on || row0 + c0 >= a.inter) continue;
                             float h[32], amax = 0.f;
 #pragma unroll
-                            for (int c = 0; c < 32; ++c) {
-                                float gt = __uint_as_float(g[c]), up = __uint_as_float(u[c]);
-                                if (a.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
-                                h[c] = swiglu_bf16(gt, up, pw, a.limit);
-                                amax = fmaxf(amax, fabsf(h[c]));
+                            for (int cc = 0; cc < 32; ++cc) {
+                                float gt = __uint_as_float(g[cc]), up = __uint_as_float(u[cc]);
+                                if (P.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
+                                h[cc] = swiglu_bf16(gt, up, pw, a.limit);
+                                amax = fmaxf(amax, fabsf(h[cc]));
                             }
                             const float sc = fp8_group_scale_bf16(amax);  // amax is a bf16 value
                             const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
                             const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact (sc is a power of two)
                             uint32_t o[8];
 #pragma unroll
-                            for (int c = 0; c < 8; ++c) {
+                            for (int cc = 0; cc < 8; ++cc) {
                                 uint32_t v = 0;
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
-                                    const float qv = fminf(fmaxf(h[4 * c + e] * inv, -448.f), 448.f);
+                                    const float qv = fminf(fmaxf(h[4 * cc + e] * inv, -448.f), 448.f);
                                     v |= (uint32_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3) << (8 * e);
                                 }
-                                o[c] = v;
+                                o[cc] = v;
                             }
-                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.out) + orow * a.out_ld + row0 + c0);
+                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.out) + orow * P.out_ld + row0 + c0);
                             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
                             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-                            a.out_sf[orow * a.out_sf_ld + ((row0 + c0) >> 5)] = (uint8_t)sb;
+                            P.out_sf[orow * P.out_sf_ld + ((row0 + c0) >> 5)] = (uint8_t)sb;
                         }
                     } else {
                         for (int c0 = egrp * 16; c0 < NW; c0 += 32) {
@@ -377,34 +408,34 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                             tc_wait_ld();
                             if (!tok_on) continue;
                             const int nrow = row0 + c0;
-                            if (nrow + 16 <= a.N) {
-                                if (a.epi == MX_EPI_STORE_F32) {
-                                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow);
+                            if (nrow + 16 <= P.N) {
+                                if (P.epi == MX_EPI_STORE_F32) {
+                                    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(P.out) + orow * P.out_ld + nrow);
 #pragma unroll
-                                    for (int c = 0; c < 4; ++c)
-                                        dst[c] = make_float4(__uint_as_float(g[4 * c]) * pw, __uint_as_float(g[4 * c + 1]) * pw, __uint_as_float(g[4 * c + 2]) * pw,
-                                                             __uint_as_float(g[4 * c + 3]) * pw);
-                                } else if (a.epi == MX_EPI_ATOMIC_F32) {
-                                    float* dst = reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow;
+                                    for (int cc = 0; cc < 4; ++cc)
+                                        dst[cc] = make_float4(__uint_as_float(g[4 * cc]) * pw, __uint_as_float(g[4 * cc + 1]) * pw,
+                                                              __uint_as_float(g[4 * cc + 2]) * pw, __uint_as_float(g[4 * cc + 3]) * pw);
+                                } else if (P.epi == MX_EPI_ATOMIC_F32) {
+                                    float* dst = reinterpret_cast<float*>(P.out) + orow * P.out_ld + nrow;
 #pragma unroll
-                                    for (int c = 0; c < 4; ++c)  // one 16-byte reduction instead of four scalar ones
-                                        red_add_v4(dst + 4 * c, __uint_as_float(g[4 * c]) * pw, __uint_as_float(g[4 * c + 1]) * pw,
-                                                   __uint_as_float(g[4 * c + 2]) * pw, __uint_as_float(g[4 * c + 3]) * pw);
+                                    for (int cc = 0; cc < 4; ++cc)  // one 16-byte reduction instead of four scalar ones
+                                        red_add_v4(dst + 4 * cc, __uint_as_float(g[4 * cc]) * pw, __uint_as_float(g[4 * cc + 1]) * pw,
+                                                   __uint_as_float(g[4 * cc + 2]) * pw, __uint_as_float(g[4 * cc + 3]) * pw);
                                 } else {
                                     uint32_t o[8];
 #pragma unroll
-                                    for (int c = 0; c < 8; ++c)
-                                        o[c] = f32_to_bf16_bits(__uint_as_float(g[2 * c]) * pw) | (f32_to_bf16_bits(__uint_as_float(g[2 * c + 1]) * pw) << 16);
-                                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + orow * a.out_ld + nrow);
+                                    for (int cc = 0; cc < 8; ++cc)
+                                        o[cc] = f32_to_bf16_bits(__uint_as_float(g[2 * cc]) * pw) | (f32_to_bf16_bits(__uint_as_float(g[2 * cc + 1]) * pw) << 16);
+                                    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(P.out) + orow * P.out_ld + nrow);
                                     dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
                                     dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
                                 }
                             } else {  // ragged last tile
-                                for (int c = 0; c < 16 && nrow + c < a.N; ++c) {
-                                    const float v = __uint_as_float(g[c]) * pw;
-                                    if (a.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(a.out)[orow * a.out_ld + nrow + c] = v;
-                                    else if (a.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(a.out) + orow * a.out_ld + nrow + c, v);
-                                    else reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + nrow + c] = __float2bfloat16_rn(v);
+                                for (int cc = 0; cc < 16 && nrow + cc < P.N; ++cc) {
+                                    const float v = __uint_as_float(g[cc]) * pw;
+                                    if (P.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(P.out)[orow * P.out_ld + nrow + cc] = v;
+                                    else if (P.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(P.out) + orow * P.out_ld + nrow + cc, v);
+                                    else reinterpret_cast<__nv_bfloat16*>(P.out)[orow * P.out_ld + nrow + cc] = __float2bfloat16_rn(v);
                                 }
                             }
                         }
@@ -413,7 +444,6 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_acc_empty(buf));  // the accumulator buffer may be overwritten once all 8 warps have read it
-                if (++it == ipw) { it = 0; ++wk; if (item + 1 < hi) w = get_work(wk); }
             }
         }
     }
@@ -493,21 +523,47 @@ static int make_tmap(CUtensorMap* tm, CUtensorMapDataType dt, int rank, const vo
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
 }
 
+static int check_prob(const MxArgs& a, const MxProb& p) {
+    if (!p.w || !p.s || !p.x8 || !p.xsf || !p.out) return ERR_BAD_ARG;
+    if (p.a_fmt != MX_A_E2M1 && p.a_fmt != MX_A_E4M3) return ERR_UNSUPPORTED;
+    if (p.N <= 0) return ERR_BAD_SHAPE;
+    if (a.dual && (p.epi != MX_EPI_SWIGLU_Q8 || p.N != 2 * a.inter || !p.out_sf)) return ERR_BAD_SHAPE;
+    if (!a.dual && p.epi == MX_EPI_SWIGLU_Q8) return ERR_BAD_SHAPE;
+    if (((uintptr_t)p.w & 31) || (p.w_estride & 31) || ((uintptr_t)p.x8 & 15) || ((uintptr_t)p.s & 3) || (p.s_rstride & 3) || (p.s_estride & 3) ||
+        ((uintptr_t)p.xsf & 3) || (p.xsf_ld & 3))
+        return ERR_BAD_ALIGN;
+    if (p.epi == MX_EPI_SWIGLU_Q8 && (((uintptr_t)p.out & 15) || (p.out_ld & 15))) return ERR_BAD_ALIGN;
+    if (p.epi != MX_EPI_SWIGLU_Q8 && (((uintptr_t)p.out & 15) || (p.out_ld & 7))) return ERR_BAD_ALIGN;
+    if (!p.work && (p.n_work || p.dense_rows <= 0)) return ERR_BAD_ARG;
+    return 0;
+}
+
+static int make_prob_tmaps(const MxArgs& a, const MxProb& p, CUtensorMap* tm_w, CUtensorMap* tm_x) {
+    const bool fp4 = p.a_fmt == MX_A_E2M1;
+    const uint64_t row_bytes = fp4 ? (uint64_t)a.K / 2 : (uint64_t)a.K;
+    const uint64_t experts = p.n_experts > 0 ? p.n_experts : 1;
+    cuuint64_t dims[3] = {(cuuint64_t)a.K, (cuuint64_t)p.N, experts};
+    cuuint64_t strides[2] = {row_bytes, (experts == 1 || p.w_estride == 0) ? row_bytes * (uint64_t)p.N : (cuuint64_t)p.w_estride};
+    cuuint32_t box[3] = {128, (cuuint32_t)a.rows_a, 1};
+    int rc = make_tmap(tm_w, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, p.w, dims, strides, box);
+    if (rc) return rc;
+    cuuint64_t xdims[2] = {(cuuint64_t)a.K, (cuuint64_t)(p.x8_rows > 0 ? p.x8_rows : 1)};
+    cuuint64_t xstrides[1] = {(cuuint64_t)a.K};
+    cuuint32_t xbox[2] = {128, (cuuint32_t)a.nd};
+    return make_tmap(tm_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p.x8, xdims, xstrides, xbox);
+}
+
 int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     MxArgs a = a_in;
-    if (!a.w || !a.s || !a.x8 || !a.xsf || !a.out) return ERR_BAD_ARG;
-    if (a.a_fmt != MX_A_E2M1 && a.a_fmt != MX_A_E4M3) return ERR_UNSUPPORTED;
-    if (a.K <= 0 || a.K % 128 || a.N <= 0) return ERR_BAD_SHAPE;
+    if (a.n_prob < 1 || a.n_prob > 2) return ERR_BAD_ARG;
+    if (a.K <= 0 || a.K % 128) return ERR_BAD_SHAPE;
     if (a.nd < 16 || a.nd > 128 || a.nd % 16) return ERR_BAD_SHAPE;
     if (a.rows_a < 32 || a.rows_a % 32 || a.rows_a * (a.dual ? 2 : 1) > 256) return ERR_BAD_SHAPE;
-    if (a.dual && (a.epi != MX_EPI_SWIGLU_Q8 || a.inter <= 0 || a.inter % 32 || a.N != 2 * a.inter || !a.out_sf)) return ERR_BAD_SHAPE;
-    if (!a.dual && a.epi == MX_EPI_SWIGLU_Q8) return ERR_BAD_SHAPE;
-    if (((uintptr_t)a.w & 31) || (a.w_estride & 31) || ((uintptr_t)a.x8 & 15) || ((uintptr_t)a.s & 3) || (a.s_rstride & 3) || (a.s_estride & 3) ||
-        ((uintptr_t)a.xsf & 3) || (a.xsf_ld & 3))
-        return ERR_BAD_ALIGN;
-    if (a.epi == MX_EPI_SWIGLU_Q8 && (((uintptr_t)a.out & 15) || (a.out_ld & 15))) return ERR_BAD_ALIGN;
-    if ((a.epi == MX_EPI_STORE_F32 || a.epi == MX_EPI_STORE_BF16 || a.epi == MX_EPI_ATOMIC_F32) && (((uintptr_t)a.out & 15) || (a.out_ld & 7))) return ERR_BAD_ALIGN;
-    if (!a.work && (a.n_work || a.dense_rows <= 0)) return ERR_BAD_ARG;
+    if (a.dual && (a.inter <= 0 || a.inter % 32)) return ERR_BAD_SHAPE;
+    for (int i = 0; i < a.n_prob; ++i) {
+        const int rc = check_prob(a, a.p[i]);
+        if (rc) return rc;
+    }
     const int NW = a.dual ? 2 * a.rows_a : a.rows_a;
     const int n_atoms = 1 + (NW + 127) / 128;
     // pipeline geometry: every stage costs a fixed round of barrier hand-offs, so stages are made as fat as a ring of two allows
@@ -521,7 +577,7 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
         sf_stage = (size_t)a.kb * n_atoms * 512;
         stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
         if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
-        // scale columns in TMEM: stages * kb * n_atoms * 4 <= 256
+        // scale columns in TMEM behind the accumulator buffers
         while (stages > 1 && stages * a.kb * n_atoms * 4 > MX_TMEM_COLS - (2 * NW <= MX_ACC_COLS_MAX ? 2 : 1) * NW) --stages;
         if (stages >= 2 || a.kb == 1) break;
     }
@@ -530,22 +586,9 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     size_t smem = (size_t)stages * (stage + sf_stage) + slack;
     if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: each CTA allocates all 512 TMEM columns
 
-    alignas(64) CUtensorMap tm_a, tm_b;
-    const bool fp4 = a.a_fmt == MX_A_E2M1;
-    const uint64_t row_bytes = fp4 ? (uint64_t)a.K / 2 : (uint64_t)a.K;
-    {
-        const uint64_t experts = a.n_experts > 0 ? a.n_experts : 1;
-        cuuint64_t dims[3] = {(cuuint64_t)a.K, (cuuint64_t)a.N, experts};
-        cuuint64_t strides[2] = {row_bytes, (experts == 1 || a.w_estride == 0) ? row_bytes * (uint64_t)a.N : (cuuint64_t)a.w_estride};
-        cuuint32_t box[3] = {128, (cuuint32_t)a.rows_a, 1};
-        int rc = make_tmap(&tm_a, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.w, dims, strides, box);
-        if (rc) return rc;
-    }
-    {
-        cuuint64_t dims[2] = {(cuuint64_t)a.K, (cuuint64_t)(a.x8_rows > 0 ? a.x8_rows : 1)};
-        cuuint64_t strides[1] = {(cuuint64_t)a.K};
-        cuuint32_t box[2] = {128, (cuuint32_t)a.nd};
-        int rc = make_tmap(&tm_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.x8, dims, strides, box);
+    alignas(64) CUtensorMap tm[4];
+    for (int i = 0; i < 2; ++i) {
+        const int rc = make_prob_tmaps(a, a.p[i < a.n_prob ? i : 0], &tm[2 * i], &tm[2 * i + 1]);
         if (rc) return rc;
     }
     static bool attr_done[64];
@@ -556,7 +599,7 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    mx_gemm_kernel<<<sm_count(), MX_THREADS, smem, stream>>>(a, tm_a, tm_b);
+    mx_gemm_kernel<<<sm_count(), MX_THREADS, smem, stream>>>(a, tm[0], tm[1], tm[2], tm[3]);
     B200_CHECK_LAUNCH();
     return 0;
 }

@@ -15,42 +15,50 @@ constexpr int MX_SMEM_LIMIT = 227 * 1024 - 2048;
 enum { MX_EPI_STORE_F32 = 0, MX_EPI_SWIGLU_Q8 = 1, MX_EPI_STORE_BF16 = 2, MX_EPI_ATOMIC_F32 = 3 };
 enum { MX_A_E4M3 = 0, MX_A_E2M1 = 5 };  // operand format codes of the tensor-core instruction descriptor
 
-struct MxArgs {
-    // A = weights [experts][N rows][K], packed E2M1 (two per byte) or e4m3 bytes
+// One GEMM problem of a launch: a weight set against activation rows.
+struct MxProb {
+    // weights [experts][N rows][K], packed E2M1 (two per byte) or e4m3 bytes
     const void* w;
     long long w_estride;    // bytes between experts
     int n_experts;
-    int a_fmt;              // MX_A_E2M1 / MX_A_E4M3
+    int a_fmt;              // MX_A_E2M1 / MX_A_E4M3 (operand format code of the weights)
     const uint8_t* s;       // E8M0 scale bytes, one per (scale row, 32 k)
     long long s_estride;    // bytes between experts
     int s_rstride;          // bytes between scale rows
     int s_row_shift;        // scale row of weight row r = r >> s_row_shift (0: per row, 5: per 32 rows)
-    int N, K;
-    // B = activations as e4m3 bytes [rows][K] with E8M0 scale bytes [rows][K/32]
+    int N;
+    // activations as e4m3 bytes [rows][K] with E8M0 scale bytes [rows][K/32]
     const uint8_t* x8;
     long long x8_rows;      // rows the buffer holds (bound of the tensor map)
     const uint8_t* xsf;
     int xsf_ld;
-    // works: {local expert, first B row, rows (1..nd), -}; nullptr = dense mode over dense_rows rows, expert 0
+    // works: {local expert, first activation row, rows (1..nd), -}; nullptr = dense mode over dense_rows rows, expert 0
     const int4* work;
     const int* n_work;
     int n_work_host;
     int dense_rows;
+    int epi;
+    const int* pair_out;    // output row of activation row p (nullptr: p)
+    const float* pair_w;    // optional weight per activation row
+    void* out;              // f32 / bf16 [rows][N] or, for SWIGLU, e4m3 bytes [rows][inter]
+    long long out_ld;
+    uint8_t* out_sf;        // SWIGLU: E8M0 scale bytes [rows][inter/32]
+    int out_sf_ld;
+    int round_gu_bf16;
+};
+
+// A launch: one or two problems with the same K, tile shape and epilogue family (both SWIGLU, or both stores).
+struct MxArgs {
+    MxProb p[2];
+    int n_prob;
+    int K;
     int nd;                 // tokens per work = token rows fetched per tile (multiple of 16, <= 128; the tile spans 128 accumulator lanes)
     int rows_a;             // weight rows per tile half: the MMA covers rows_a (single) or 2 * rows_a (dual) weight rows
     int dual;               // 1: gate rows r and up rows inter + r side by side in one tile, epilogue SWIGLU
     int kb;                 // 128-wide k blocks per pipeline stage
     int n_stages;
-    int epi;
-    const int* pair_out;    // output row of B row p (nullptr: p)
-    const float* pair_w;    // optional weight per B row
-    void* out;              // f32 / bf16 [rows][N] or, for SWIGLU, e4m3 bytes [rows][inter]
-    long long out_ld;
-    uint8_t* out_sf;        // SWIGLU: E8M0 scale bytes [rows][inter/32]
-    int out_sf_ld;
     float limit;
     int inter;
-    int round_gu_bf16;
 };
 
 int mx_launch(const MxArgs& a, cudaStream_t stream);

@@ -35,7 +35,7 @@ class MoELayer:
         self.topk, self.gate_bias, self.gate_temp, self.route_scale = topk, gate_bias, gate_temp, route_scale
         self.score_func, self.norm, self.swiglu_limit = score_func, norm_topk_prob and topk > 1, swiglu_limit
         self.device = dev
-        # engine 0 = automatic (weight streaming up to 8 tokens, block-scaled tensor cores beyond), 1 = weight streaming with
+        # engine 0 = automatic (weight streaming up to 4 tokens, block-scaled tensor cores beyond), 1 = weight streaming with
         # in-register dequantisation, 2 = block-scaled tensor cores.  The tensor-core path reads the shared expert in natural k
         # order, so a natural-order copy is kept next to the W8 container.
         self.engine = engine
@@ -48,7 +48,7 @@ class MoELayer:
             self._sh_nat = (unpermute_k(sh_w13.w8), unpermute_k(sh_w2.w8))
 
     def _use_mx(self, tokens: int) -> bool:
-        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 8)
+        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 4)
 
     def shared_expert(self, x: torch.Tensor) -> torch.Tensor | None:
         """The shared expert alone: x bf16 [T, D] -> ys bf16 [T, D] (None without one); the values of dsv41/model.py:1635-1638 on FP8
