@@ -63,6 +63,8 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+// named barrier of the eight epilogue warps
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -117,6 +119,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     uint8_t* ring = base;
     uint8_t* sf_ring = base + (size_t)NS * stage_bytes;   // per stage: [kb][n_atoms] atoms of 512 B
     const uint32_t sf_stage_bytes = (uint32_t)(KB * n_atoms) * 512u;
+    float* stg = reinterpret_cast<float*>(sf_ring + (size_t)NS * sf_stage_bytes);  // staging of small accumulator tiles: [32 tokens][MX_STG_LD]
     auto bar_full_ab = [&](int s) { return smem_u32(&bars[s]); };
     auto bar_full_sf = [&](int s) { return smem_u32(&bars[MX_MAX_STAGES + s]); };
     auto bar_empty = [&](int s) { return smem_u32(&bars[2 * MX_MAX_STAGES + s]); };
@@ -350,7 +353,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
             const int t = q * 32 + lane;
             ItemCur c = locate(lo, true);
             uint32_t acc_it = 0;
-            for (; c.item < hi && !abort_flag; next_item(c, true), ++acc_it) {
+            // No early exit from this loop: the eight warps meet at named barriers, so all of them walk the same item sequence;
+            // once a wait has run out of time every later wait returns at once and the loop drains quickly.
+            for (; c.item < hi; next_item(c, true), ++acc_it) {
                 const MxProb& P = a.p[c.pr];
                 const int4 w = c.w;
                 const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
@@ -363,6 +368,46 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 const float pw = (P.pair_w && tok_on) ? __ldg(P.pair_w + prow) : 1.f;
                 const long orow = (P.pair_out && tok_on) ? (long)__ldg(P.pair_out + prow) : (long)prow;
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
+                if (P.epi == MX_EPI_SWIGLU_Q8 && w.z <= a.stg_rows) {
+                    // ---- few tokens: a thread per token would leave most lanes idle for the whole SwiGLU.  The two warps that can
+                    // read TMEM lanes 0-31 copy the tile to shared memory, the accumulator is handed back to the MMA issuer at once,
+                    // and all eight warps then work on (token, group of 32 columns) tasks with one column per lane.
+                    epi_bar();  // the tasks of the previous small tile are done: the staging buffer may be overwritten
+                    if (ready && q == 0) {
+                        const int cbase = egrp * (NW / 2);
+                        for (int c0 = 0; c0 < NW / 2; c0 += 16) {
+                            uint32_t g[16];
+                            tc_ld16(t0 + cbase + c0, g);
+                            tc_wait_ld();
+                            if (lane < a.stg_rows)  // the buffer holds stg_rows token rows
+#pragma unroll
+                                for (int cc = 0; cc < 16; ++cc) stg[lane * MX_STG_LD + cbase + c0 + cc] = __uint_as_float(g[cc]);
+                        }
+                    }
+                    tc_fence_before();
+                    epi_bar();  // the copy is visible to all epilogue warps
+                    if (lane == 0) mbar_arrive(bar_acc_empty(buf));
+                    const int ngrp = rows_w >> 5, ew = q + 4 * egrp;
+                    if (ready) {
+                        for (int task = ew; task < w.z * ngrp; task += 8) {
+                            const int tk = task / ngrp, gi = task - tk * ngrp;
+                            if (row0 + gi * 32 >= a.inter) continue;
+                            const int col = gi * 32 + lane;
+                            float gt = stg[tk * MX_STG_LD + col], up = stg[tk * MX_STG_LD + rows_w + col];
+                            if (P.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
+                            const int pr_row = w.y + tk;
+                            const float pwt = P.pair_w ? __ldg(P.pair_w + pr_row) : 1.f;
+                            const long orw = P.pair_out ? (long)__ldg(P.pair_out + pr_row) : (long)pr_row;
+                            const float h = swiglu_bf16(gt, up, pwt, a.limit);
+                            const float sc = fp8_group_scale_bf16(warp_max(fabsf(h)));
+                            const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
+                            const float qv = fminf(fmaxf(h * u32_as_f32((254u - sb) << 23), -448.f), 448.f);
+                            reinterpret_cast<uint8_t*>(P.out)[orw * P.out_ld + row0 + col] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
+                            if (lane == 0) P.out_sf[orw * P.out_sf_ld + ((row0 + gi * 32) >> 5)] = (uint8_t)sb;
+                        }
+                    }
+                    continue;
+                }
                 if (warp_on) {
                     if (P.epi == MX_EPI_SWIGLU_Q8) {
                         // columns c = SwiGLU column row0 + c; 32 consecutive columns are one quantisation group (dsv41/fused.py:285-306)
@@ -566,21 +611,32 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
     }
     const int NW = a.dual ? 2 * a.rows_a : a.rows_a;
     const int n_atoms = 1 + (NW + 127) / 128;
-    // pipeline geometry: every stage costs a fixed round of barrier hand-offs, so stages are made as fat as a ring of two allows
-    // (measured: two k blocks per stage, two stages beat one k block per stage, four or five stages)
-    const size_t slack = 1024 + 16384;  // the token descriptors always span 128 rows: slack behind the ring for boxes with fewer rows
-    if (a.kb < 1 || a.kb > 4) a.kb = 4;
-    int stages = 0;
-    size_t stage = 0, sf_stage = 0;
-    for (;; --a.kb) {
-        stage = (size_t)a.kb * ((size_t)a.nd * 128 + (size_t)NW * 128);
-        sf_stage = (size_t)a.kb * n_atoms * 512;
-        stages = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
-        if (stages > MX_MAX_STAGES) stages = MX_MAX_STAGES;
+    // pipeline geometry.  Every stage costs a fixed round of barrier hand-offs, so stages are fat (two or more k blocks) when a ring
+    // of three of them fits, which also keeps enough bytes in flight to cover the DRAM latency; otherwise two fat stages, which
+    // measured faster than four or five thin ones.
+    auto ring_for = [&](int kb, size_t& stage, size_t& sf_stage, size_t& slack) -> int {
+        stage = (size_t)kb * ((size_t)a.nd * 128 + (size_t)NW * 128);
+        sf_stage = (size_t)kb * n_atoms * 512;
+        // 1 KB to align the ring; the token descriptors always span 128 rows (16 KB) from the start of a token box, which stays
+        // inside the stage unless the stage is very small
+        const size_t span = (size_t)a.nd * 128 + (size_t)kb * NW * 128;
+        slack = 1024 + (span < 16384 ? 16384 - span : 0);  // + the staging buffer of the small-tile epilogue
+        slack += (size_t)a.stg_rows * MX_STG_LD * 4;
+        int st = (int)(((size_t)MX_SMEM_LIMIT - slack) / (stage + sf_stage));
+        if (st > MX_MAX_STAGES) st = MX_MAX_STAGES;
         // scale columns in TMEM behind the accumulator buffers
-        while (stages > 1 && stages * a.kb * n_atoms * 4 > MX_TMEM_COLS - (2 * NW <= MX_ACC_COLS_MAX ? 2 : 1) * NW) --stages;
-        if (stages >= 2 || a.kb == 1) break;
-    }
+        while (st > 1 && st * kb * n_atoms * 4 > MX_TMEM_COLS - (2 * NW <= MX_ACC_COLS_MAX ? 2 : 1) * NW) --st;
+        return st;
+    };
+    // small-tile staging: 32 token rows when works are that small anyway, else 16 (the ring needs the shared memory more)
+    a.stg_rows = a.nd <= 32 ? 32 : 16;
+    int stages = 0;
+    size_t stage = 0, sf_stage = 0, slack = 0;
+    a.kb = 0;
+    for (int kb = 4; kb >= 2 && !a.kb; --kb)
+        if ((stages = ring_for(kb, stage, sf_stage, slack)) >= 3) a.kb = kb;
+    if (!a.kb && (stages = ring_for(2, stage, sf_stage, slack)) >= 2) a.kb = 2;
+    if (!a.kb) { stages = ring_for(1, stage, sf_stage, slack); a.kb = 1; }
     if (stages < 2) return ERR_BAD_SHAPE;
     a.n_stages = stages;
     size_t smem = (size_t)stages * (stage + sf_stage) + slack;

@@ -10,7 +10,9 @@ constexpr int MX_THREADS = 512;   // 16 warps: TMA producer, MMA issuer, 2 spare
 constexpr int MX_TMEM_COLS = 512;
 constexpr int MX_ACC_COLS_MAX = 384;  // TMEM columns the accumulator buffers may take; the rest holds the scale factors
 constexpr int MX_MAX_STAGES = 8;
-constexpr int MX_SMEM_LIMIT = 227 * 1024 - 2048;
+constexpr int MX_STG_LD = 257;                      // row stride (floats) of the small-tile staging buffer: odd, so that both the
+                                                    // per-token writes and the per-column reads are free of bank conflicts
+constexpr int MX_SMEM_LIMIT = 227 * 1024 - 1024;  // dynamic shared memory: the 227 KB a block may use minus the kernel's static 1 KB
 
 enum { MX_EPI_STORE_F32 = 0, MX_EPI_SWIGLU_Q8 = 1, MX_EPI_STORE_BF16 = 2, MX_EPI_ATOMIC_F32 = 3 };
 enum { MX_A_E4M3 = 0, MX_A_E2M1 = 5 };  // operand format codes of the tensor-core instruction descriptor
@@ -57,6 +59,7 @@ struct MxArgs {
     int dual;               // 1: gate rows r and up rows inter + r side by side in one tile, epilogue SWIGLU
     int kb;                 // 128-wide k blocks per pipeline stage
     int n_stages;
+    int stg_rows;           // token rows of the small-tile staging buffer (set by mx_launch): works up to this size take the staged epilogue
     float limit;
     int inter;
 };
