@@ -368,8 +368,8 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 const float pw = (P.pair_w && tok_on) ? __ldg(P.pair_w + prow) : 1.f;
                 const long orow = (P.pair_out && tok_on) ? (long)__ldg(P.pair_out + prow) : (long)prow;
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
-                if (P.epi == MX_EPI_SWIGLU_Q8 && w.z <= a.stg_rows) {
-                    // ---- few tokens: a thread per token would leave most lanes idle for the whole SwiGLU.  The two warps that can
+                if (w.z <= a.stg_rows) {
+                    // ---- few tokens: a thread per token would leave most lanes idle for the whole epilogue.  The two warps that can
                     // read TMEM lanes 0-31 copy the tile to shared memory, the accumulator is handed back to the MMA issuer at once,
                     // and all eight warps then work on (token, group of 32 columns) tasks with one column per lane.
                     epi_bar();  // the tasks of the previous small tile are done: the staging buffer may be overwritten
@@ -387,8 +387,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                     tc_fence_before();
                     epi_bar();  // the copy is visible to all epilogue warps
                     if (lane == 0) mbar_arrive(bar_acc_empty(buf));
-                    const int ngrp = rows_w >> 5, ew = q + 4 * egrp;
-                    if (ready) {
+                    const int ew = q + 4 * egrp;
+                    if (ready && P.epi == MX_EPI_SWIGLU_Q8) {
+                        const int ngrp = rows_w >> 5;
                         for (int task = ew; task < w.z * ngrp; task += 8) {
                             const int tk = task / ngrp, gi = task - tk * ngrp;
                             if (row0 + gi * 32 >= a.inter) continue;
@@ -404,6 +405,19 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                             const float qv = fminf(fmaxf(h * u32_as_f32((254u - sb) << 23), -448.f), 448.f);
                             reinterpret_cast<uint8_t*>(P.out)[orw * P.out_ld + row0 + col] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
                             if (lane == 0) P.out_sf[orw * P.out_sf_ld + ((row0 + gi * 32) >> 5)] = (uint8_t)sb;
+                        }
+                    } else if (ready) {
+                        const int nch = NW >> 5;  // 32-column chunks: a warp stores 128 contiguous bytes (fp32) per task
+                        for (int task = ew; task < w.z * nch; task += 8) {
+                            const int tk = task / nch, col = (task - tk * nch) * 32 + lane;
+                            if (row0 + col >= P.N) continue;
+                            const int pr_row = w.y + tk;
+                            const float pwt = P.pair_w ? __ldg(P.pair_w + pr_row) : 1.f;
+                            const long orw = P.pair_out ? (long)__ldg(P.pair_out + pr_row) : (long)pr_row;
+                            const float v = stg[tk * MX_STG_LD + col] * pwt;
+                            if (P.epi == MX_EPI_STORE_F32) reinterpret_cast<float*>(P.out)[orw * P.out_ld + row0 + col] = v;
+                            else if (P.epi == MX_EPI_ATOMIC_F32) atomicAdd(reinterpret_cast<float*>(P.out) + orw * P.out_ld + row0 + col, v);
+                            else reinterpret_cast<__nv_bfloat16*>(P.out)[orw * P.out_ld + row0 + col] = __float2bfloat16_rn(v);
                         }
                     }
                     continue;
