@@ -334,15 +334,21 @@ def run_gpu(args):
     value = S / (ms * 1e-3)
 
     # ---- e2e: host buffers, copies inside the timed region
-    xh = [x[first:first + T_r].contiguous().pin_memory() for x in xs_h]
-    lh = [l[first:first + T_r].contiguous().pin_memory() for l in ls_h]
+    # a step's inputs (token rows + router logits) sit in ONE pinned host buffer, so that they cross PCIe in one copy
+    nbx, nbl = xs[0].numel() * xs[0].element_size(), ls[0].numel() * ls[0].element_size()
+    hb = []
+    for x, l in zip(xs_h, ls_h):
+        b = torch.empty(nbx + nbl, dtype=torch.uint8).pin_memory()
+        b[:nbx].copy_(x[first:first + T_r].contiguous().view(torch.uint8).reshape(-1))
+        b[nbx:].copy_(l[first:first + T_r].contiguous().view(torch.uint8).reshape(-1))
+        hb.append(b)
     oh = torch.empty(T_r, D, dtype=torch.bfloat16).pin_memory()
-    xd, ld = torch.empty_like(xs[0]), torch.empty_like(ls[0])
+    db = torch.empty(nbx + nbl, dtype=torch.uint8, device=dev)
+    xd = db[:nbx].view(xs[0].dtype).view(xs[0].shape)
+    ld = db[nbx:].view(ls[0].dtype).view(ls[0].shape)
 
     def step_e2e(i):
-        j = i % NP
-        xd.copy_(xh[j], non_blocking=True)
-        ld.copy_(lh[j], non_blocking=True)
+        db.copy_(hb[i % NP], non_blocking=True)
         if world == 1:
             layer.forward(xd, ld, out=out)
         else:
@@ -350,7 +356,7 @@ def run_gpu(args):
         oh.copy_(out, non_blocking=True)
 
     ms_e2e = max_over_ranks(time_steps(step_e2e, args.steps, args.warmup, barrier))
-    h2d = T_r * (D * 2 + E * 2) * world
+    h2d = (nbx + nbl) * world
     d2h = T_r * D * 2 * world
 
     if rank != 0:
@@ -375,7 +381,12 @@ def run_gpu(args):
             # the tensor-core launch streams the shared expert's gate/up matrix (FP8 + 32x32 scales) in the same kernel
             alg = statistics.mean(u_steps) * exp_b13 + ((2 * I * D + 2 * I * D // 1024) if mx else 0)
             achieved = alg / (avg_ms * 1e-3) / 1e9
-            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            # DRAM bytes per launch: (dram__bytes_read + dram__bytes_write) / algorithmic bytes of the same kernel in the committed ncu
+            # captures (profiles/mx_gemm_kernel_decode64_e96_ncu_full.md: 0.990; profiles/skinny_fp4_decode8_ncu_full.md: 1.075),
+            # scaled to this launch by its algorithmic bytes (traffic grows with the experts streamed)
+            traffic = alg * (0.990 if mx else 1.075)
+            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+                                "traffic_source": "ncu capture of a smaller case, scaled by algorithmic bytes",
                                 "kernel": ("mx_gemm_kernel (gate/up weight stream of the routed experts and the shared expert on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)" if mx
                                            else "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"),
                                 "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
