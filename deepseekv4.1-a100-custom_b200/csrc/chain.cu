@@ -13,7 +13,7 @@ namespace b200 {
 constexpr int ROUTE_THREADS = 128;
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
-constexpr int MX_AUTO_MIN_TOKENS = 4;   // automatic engine choice: up to this many tokens the weight-streaming kernels are faster (measured)
+constexpr int MX_AUTO_MIN_TOKENS = 0;   // automatic engine choice: the tensor-core kernels serve every batch size whose formats they accept
 constexpr int MX_ND_DECODE = 32;        // tokens per work of the block-scaled tensor-core path
 
 struct RouteArgs {
@@ -394,12 +394,13 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     const bool small = P <= ROUTE_MAX_PAIRS;
     // engine: 1 = weight streaming with in-register dequantisation (any scale format, decode-sized batches only),
     //         2 = block-scaled tensor cores (E8M0 scales, natural k order of the shared expert), 0 = automatic:
-    //         streaming for the smallest batches (<= MX_AUTO_MIN_TOKENS tokens), tensor cores beyond
+    //         tensor cores whenever the formats allow (measured faster from one token up), else streaming
     const bool mx_ok = m->expert_fmt == SK_FMT_FP4_E8M0 && (!m->has_shared || (m->shared_fmt == SK_FMT_FP8_E8M0 && !m->sh_permk));
     if ((m->engine == 2 || !small) && !mx_ok) return ERR_UNSUPPORTED;
     if (m->engine == 1 && !small) return ERR_UNSUPPORTED;
     const bool use_mx = m->engine == 2 || !small || (m->engine == 0 && mx_ok && T > MX_AUTO_MIN_TOKENS);
-    const bool shared = m->has_shared && m->out;
+    const bool shared = m->has_shared && (m->out || m->shared_out);
+    __nv_bfloat16* const ys_buf = m->shared_out ? (__nv_bfloat16*)m->shared_out : w.ys;  // the shared expert's result
     cudaError_t ce;
     int rc;
 
@@ -435,9 +436,9 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         // activations -> e4m3 + E8M0 (the FP8 fake quantisation kept in quantised form), gathered into pair-sorted order
         if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream))) return rc;
         if (shared && (rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, nullptr, T, D, w.x8t, w.xsft, stream))) return rc;
-        // weight rows per tile: as many as the tensor-core instruction takes (256) once there are enough (work, tile) items to
-        // balance over the SMs; fewer rows per tile for the smallest batches
-        const int rows1 = P >= 48 ? 128 : (P >= 24 ? 64 : 32), rows2 = 2 * rows1;
+        // always the widest tiles (256 weight rows per MMA): even when that leaves fewer (work, tile) items than SMs, as for a single
+        // token (6 works x 16 tiles), the wide tiles stream faster than more, narrower ones (measured 83 us against 136 us per step)
+        const int rows1 = 128, rows2 = 256;
         // each GEMM launch carries the routed experts (problem 0) and, behind them in the same item list, the shared expert
         // (problem 1: one FP8 matrix against all tokens)
         MxArgs g1{};
@@ -480,7 +481,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             q.s = (const uint8_t*)m->sh_s2; q.s_rstride = m->sh_s2_cols; q.s_row_shift = 5;
             q.N = D; q.x8 = w.hs8; q.x8_rows = T + 128; q.xsf = w.hssf; q.xsf_ld = I / 32;
             q.work = nullptr; q.dense_rows = T; q.n_work_host = (T + nd - 1) / nd; q.epi = MX_EPI_STORE_BF16;
-            q.out = w.ys; q.out_ld = D;
+            q.out = ys_buf; q.out_ld = D;
         }
         if ((rc = mx_launch(g2, stream))) return rc;
     } else {
@@ -518,19 +519,19 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             d.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s2_cols : m->sh_s2_cols * 4;
             d.N = D; d.K = I; d.x = w.hs; d.x_ld = I; d.w_permk = m->sh_permk;
             d.work = nullptr; d.dense_rows = T; d.n_work_host = (T + SK_TOK - 1) / SK_TOK;
-            d.out = w.ys; d.out_ld = D;
+            d.out = ys_buf; d.out_ld = D;
             if ((rc = skinny_launch(d, m->shared_fmt, SK_EPI_STORE_BF16, stream))) return rc;
         }
     }
     // ---- combine: routed sum (+ shared expert) -> bf16
     const long n = (long)T * D;
     if (small) {
-        moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.y2, w.eid, shared ? w.ys : nullptr, (__nv_bfloat16*)m->out, m->routed_out, T, topk, D,
+        moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.y2, w.eid, shared ? ys_buf : nullptr, (__nv_bfloat16*)m->out, m->routed_out, T, topk, D,
                                                                            m->shard_start, shard_n);
         B200_CHECK_LAUNCH();
     } else {
         if (m->out) {
-            moe_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.acc, shared ? w.ys : nullptr, (__nv_bfloat16*)m->out, n);
+            moe_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.acc, shared ? ys_buf : nullptr, (__nv_bfloat16*)m->out, n);
             B200_CHECK_LAUNCH();
         }
         if (m->routed_out && (ce = cudaMemcpyAsync(m->routed_out, w.acc, sizeof(float) * n, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;

@@ -79,12 +79,25 @@ class EPMoE:
         else:
             dist.all_gather(list(x_all.split(counts)), x_local.contiguous(), group=self.group)
             dist.all_gather(list(l_all.split(counts)), logits_local.contiguous(), group=self.group)
-        # local experts over all tokens
-        part = self.partial_fn(x_all, l_all)  # fp32 [T, D]
-        # combine: rows of rank r's tokens go to rank r; sum the W received blocks in rank order
-        recv = torch.empty(W * T_r, part.shape[1], dtype=part.dtype, device=part.device)
-        dist.all_to_all_single(recv, part.contiguous(), output_split_sizes=[T_r] * W, input_split_sizes=counts, group=self.group)
-        routed = recv.view(W, T_r, -1).sum(dim=0) if W > 1 else recv
+        fused = self.layer is not None and self.partial_fn == self._partial_cuda and self.shared_fn == self._shared_cuda
+        if fused:
+            # local experts over all tokens; the shared expert rides in the same launches (its weight stream costs the same for all
+            # tokens as for this rank's), this rank keeps its own rows of the result
+            part, ys_all = self.layer.forward(x_all, l_all, final=False, want_routed=True, want_shared=True)
+        else:
+            part = self.partial_fn(x_all, l_all)  # fp32 [T, D]
+        # combine: rows of rank r's tokens go to rank r and are summed there
+        if even and W > 1 and part.is_cuda:
+            routed = torch.empty(T_r, part.shape[1], dtype=part.dtype, device=part.device)
+            dist.reduce_scatter_tensor(routed, part.contiguous(), group=self.group)
+        else:
+            recv = torch.empty(W * T_r, part.shape[1], dtype=part.dtype, device=part.device)
+            dist.all_to_all_single(recv, part.contiguous(), output_split_sizes=[T_r] * W, input_split_sizes=counts, group=self.group)
+            routed = recv.view(W, T_r, -1).sum(dim=0) if W > 1 else recv  # summed in rank order
+        if fused:
+            from .fused2 import moe_combine
+            first = sum(counts[:self.rank])
+            return moe_combine(routed.unsqueeze(1), ys_all[first:first + T_r] if ys_all is not None else None)
         return self.shared_fn(x_local, routed)
 
     __call__ = forward

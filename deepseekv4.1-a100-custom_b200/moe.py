@@ -35,7 +35,7 @@ class MoELayer:
         self.topk, self.gate_bias, self.gate_temp, self.route_scale = topk, gate_bias, gate_temp, route_scale
         self.score_func, self.norm, self.swiglu_limit = score_func, norm_topk_prob and topk > 1, swiglu_limit
         self.device = dev
-        # engine 0 = automatic (weight streaming up to 4 tokens, block-scaled tensor cores beyond), 1 = weight streaming with
+        # engine 0 = automatic (block-scaled tensor cores whenever the formats allow, else weight streaming), 1 = weight streaming with
         # in-register dequantisation, 2 = block-scaled tensor cores.  The tensor-core path reads the shared expert in natural k
         # order, so a natural-order copy is kept next to the W8 container.
         self.engine = engine
@@ -48,7 +48,7 @@ class MoELayer:
             self._sh_nat = (unpermute_k(sh_w13.w8), unpermute_k(sh_w2.w8))
 
     def _use_mx(self, tokens: int) -> bool:
-        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 4)
+        return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 0)
 
     def shared_expert(self, x: torch.Tensor) -> torch.Tensor | None:
         """The shared expert alone: x bf16 [T, D] -> ys bf16 [T, D] (None without one); the values of dsv41/model.py:1635-1638 on FP8
@@ -77,7 +77,7 @@ class MoELayer:
         return linear_w(hs, self.sh_w2)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, *, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
-                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, prof_events=None):
+                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, want_shared: bool = False, prof_events=None):
         """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E].
         Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
         and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel."""
@@ -103,7 +103,8 @@ class MoELayer:
         a.x, a.x_is_quantized = x.data_ptr(), int(x_is_quantized)
         a.w13, a.s13, a.w2, a.s2 = self.w13.data_ptr(), self.s13.data_ptr(), self.w2.data_ptr(), self.s2.data_ptr()
         a.expert_fmt, a.shard_start, a.shard_n = self.expert_fmt, self.shard_start, self.n_local
-        shared = with_shared and self.sh_w13 is not None and final
+        shared = with_shared and self.sh_w13 is not None and (final or want_shared)
+        ys = torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16) if (want_shared and shared) else None
         a.has_shared = int(shared)
         if shared:
             w13b, w2b = (self._sh_nat if mx else (self.sh_w13.w8, self.sh_w2.w8))
@@ -113,6 +114,7 @@ class MoELayer:
         a.swiglu_limit = float(self.swiglu_limit)
         a.out = out.data_ptr() if final else None
         a.routed_out = routed.data_ptr() if routed is not None else None
+        a.shared_out = ys.data_ptr() if ys is not None else None
         a.eid_out = eid.data_ptr() if eid is not None else None
         a.wt_out = wt.data_ptr() if wt is not None else None
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
@@ -126,6 +128,8 @@ class MoELayer:
             res.append(routed)
         if want_route:
             res += [eid, wt]
+        if want_shared:
+            res.append(ys)
         return res[0] if len(res) == 1 else tuple(res)
 
     __call__ = forward

@@ -165,6 +165,9 @@ typedef struct b200_moe_args {
     /* 0 = automatic, 1 = weight-streaming path with in-register dequantisation (any scale format), 2 = block-scaled
      * tensor-core path (tcgen05 kind::mxf8f6f4; needs E8M0 scales and the shared expert in natural k order, sh_permk = 0) */
     int engine;
+    /* optional: the shared expert's own result, bf16 [tokens, dim] (NULL = not wanted).  With has_shared it is computed even when
+     * `out` is NULL; an expert-parallel caller adds it to the routed sum it gets back from the exchange. */
+    void* shared_out;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);

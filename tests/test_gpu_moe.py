@@ -110,3 +110,38 @@ def test_layer_prefill_shard(mods, oracle, dev):
     ref = oracle.moe_layer(x, logits.float(), None, ex["w13"][4:12], ex["s13"][4:12], ex["w2"][4:12], ex["s2"][4:12], None, topk=topk, shard=(4, 8), n_experts=E)
     assert rel_err(r, ref["routed"]) <= 1e-2
     assert mods.cukern.device_error(dev) == 0
+
+
+@pytest.mark.parametrize("T,engine", [(7, 1), (7, 2), (200, 0)])
+def test_shared_expert_as_separate_output(mods, dev, T, engine):
+    # what an expert-parallel caller uses: routed partial sum and the shared expert's own result from the same launches
+    E, D, I, topk = 16, 512, 256, 4
+    _, _, layer = _layer(mods, dev, E, D, I, topk, 31, engine=engine)
+    x = mods.synth.make_tokens(T, D, 33).to(dev)
+    logits = mods.synth.make_logits(T, E, 34, topk=topk).to(dev)
+    out = layer.forward(x, logits)
+    routed, ys = layer.forward(x, logits, final=False, want_routed=True, want_shared=True)
+    assert ys.dtype == torch.bfloat16 and ys.shape == (T, D)
+    assert torch.equal(mods.fused2.moe_combine(routed.unsqueeze(1), ys), out)
+    assert rel_err(ys, layer.shared_expert(x)) < 1e-6
+    assert mods.cukern.device_error(dev) == 0
+
+
+def test_expert_parallel_layer_world_of_one_equals_layer(mods, dev):
+    # the CUDA defaults of the expert-parallel wrapper (shared expert fused into the local launches) on a one-rank group
+    import os
+    import torch.distributed as dist
+    if dist.is_initialized():
+        pytest.skip("a process group already exists in this process")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29577")
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    try:
+        E, D, I, topk, T = 16, 512, 256, 4, 12
+        _, _, layer = _layer(mods, dev, E, D, I, topk, 41)
+        x = mods.synth.make_tokens(T, D, 43).to(dev)
+        logits = mods.synth.make_logits(T, E, 44, topk=topk).to(dev)
+        got = mods.ep.EPMoE(layer).forward(x, logits)
+        assert torch.equal(got, layer.forward(x, logits))
+    finally:
+        dist.destroy_process_group()
