@@ -247,7 +247,8 @@ def build_inputs(synth, S: int, dev):
     return xs, ls
 
 
-def time_steps(fn, steps: int, warmup: int, barrier):
+def time_steps(fn, steps: int, warmup: int, barrier, finish=None):
+    """finish(): makes the current stream wait for work the steps put on other streams, so that the closing event covers it."""
     for i in range(warmup):
         fn(i)
     barrier()
@@ -256,6 +257,8 @@ def time_steps(fn, steps: int, warmup: int, barrier):
     e0.record()
     for i in range(steps):
         fn(warmup + i)
+    if finish is not None:
+        finish()
     e1.record()
     torch.cuda.synchronize()
     barrier()
@@ -342,20 +345,43 @@ def run_gpu(args):
         b[:nbx].copy_(x[first:first + T_r].contiguous().view(torch.uint8).reshape(-1))
         b[nbx:].copy_(l[first:first + T_r].contiguous().view(torch.uint8).reshape(-1))
         hb.append(b)
-    oh = torch.empty(T_r, D, dtype=torch.bfloat16).pin_memory()
-    db = torch.empty(nbx + nbl, dtype=torch.uint8, device=dev)
-    xd = db[:nbx].view(xs[0].dtype).view(xs[0].shape)
-    ld = db[nbx:].view(ls[0].dtype).view(ls[0].shape)
+    # Copies and compute are pipelined as a serving loop would: step i's inputs cross PCIe on a copy stream while step i-1 computes,
+    # and step i-1's result goes back on a third stream; two sets of device and host buffers, ordered by events.  Every step still
+    # pays its own host->device copy and its own device->host read inside the timed region.
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    oh = [torch.empty(T_r, D, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    db = [torch.empty(nbx + nbl, dtype=torch.uint8, device=dev) for _ in range(2)]
+    xd = [b[:nbx].view(xs[0].dtype).view(xs[0].shape) for b in db]
+    ld = [b[nbx:].view(ls[0].dtype).view(ls[0].shape) for b in db]
+    outs = [torch.empty_like(out) for _ in range(2)]
+    ev_in, ev_cmp, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
+    for e in ev_in + ev_cmp + ev_out:
+        e.record(cur)
 
     def step_e2e(i):
-        db.copy_(hb[i % NP], non_blocking=True)
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_cmp[b])       # the step before last has finished reading this input buffer
+            db[b].copy_(hb[i % NP], non_blocking=True)
+            ev_in[b].record(s_in)
+        cur.wait_event(ev_in[b])
+        cur.wait_event(ev_out[b])            # the step before last has left this output buffer
         if world == 1:
-            layer.forward(xd, ld, out=out)
+            layer.forward(xd[b], ld[b], out=outs[b])
         else:
-            out.copy_(epl.forward(xd, ld, counts))
-        oh.copy_(out, non_blocking=True)
+            outs[b].copy_(epl.forward(xd[b], ld[b], counts))
+        ev_cmp[b].record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_cmp[b])
+            oh[b].copy_(outs[b], non_blocking=True)
+            ev_out[b].record(s_out)
 
-    ms_e2e = max_over_ranks(time_steps(step_e2e, args.steps, args.warmup, barrier))
+    def finish_e2e():
+        cur.wait_event(ev_out[0])
+        cur.wait_event(ev_out[1])
+
+    ms_e2e = max_over_ranks(time_steps(step_e2e, args.steps, args.warmup, barrier, finish_e2e))
     h2d = (nbx + nbl) * world
     d2h = T_r * D * 2 * world
 
@@ -370,7 +396,7 @@ def run_gpu(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.workload, world), "clocks": clocks,
             "e2e": {"value": S / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
-            "gpu_launches": ((9 if S > 64 else 6) + (0 if world == 1 else 3)) * args.steps}
+            "gpu_launches": ((8 if S > 64 else (5 if layer._use_mx(T_r * world) else 6)) + (0 if world == 1 else 1)) * args.steps}
     if world == 1:
         durs = [prof[args.warmup + i][0].elapsed_time(prof[args.warmup + i][1]) for i in range(args.steps)]
         u_steps = [uniq[(args.warmup + i) % NP] for i in range(args.steps)]

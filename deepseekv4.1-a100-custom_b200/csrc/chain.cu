@@ -434,8 +434,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
 
     if (use_mx) {
         // activations -> e4m3 + E8M0 (the FP8 fake quantisation kept in quantised form), gathered into pair-sorted order
-        if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream))) return rc;
-        if (shared && (rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, nullptr, T, D, w.x8t, w.xsft, stream))) return rc;
+        // (and, for the shared expert, in token order: one launch for both)
+        if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream, shared ? T : 0, w.x8t, w.xsft))) return rc;
         // always the widest tiles (256 weight rows per MMA): even when that leaves fewer (work, tile) items than SMs, as for a single
         // token (6 works x 16 tiles), the wide tiles stream faster than more, narrower ones (measured 83 us against 136 us per step)
         const int rows1 = 128, rows2 = 256;

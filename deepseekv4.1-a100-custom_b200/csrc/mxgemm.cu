@@ -530,14 +530,22 @@ __global__ void mx_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, lon
     if (lane == 0) sf[(long)row * gpr + grp] = (uint8_t)((f32_as_u32(s) >> 23) & 0xFFu);
 }
 
-// 16-byte-aligned rows: a thread quantises 8 values (one 16-byte load), 4 threads share a group of 32
+// 16-byte-aligned rows: a thread quantises 8 values (one 16-byte load), 4 threads share a group of 32.  Two row sets in one launch:
+// rows [0, rows) gather input rows through src_row (or take row r when src_row is null) into q8 / sf, rows [rows, rows + rows2)
+// take input row r - rows into q8b / sfb (the layer quantises its pair-sorted copy and its token-order copy in one go).
 __global__ void __launch_bounds__(256) mx_quantize_rows_vec_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const int* __restrict__ src_row,
-                                                                   int rows, int K, uint8_t* __restrict__ q8, uint8_t* __restrict__ sf) {
+                                                                   int rows, int K, uint8_t* __restrict__ q8, uint8_t* __restrict__ sf, int rows2,
+                                                                   uint8_t* __restrict__ q8b, uint8_t* __restrict__ sfb) {
     const int tpr = K >> 3;  // threads per row
     const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    const bool on = gid < (long)rows * tpr;  // K % 32 == 0: the 4 threads of a group are on or off together
-    const int row = on ? (int)(gid / tpr) : 0, c8 = on ? (int)(gid % tpr) : 0;
-    const long src = src_row ? __ldg(src_row + row) : row;
+    const bool on = gid < (long)(rows + rows2) * tpr;  // K % 32 == 0: the 4 threads of a group are on or off together
+    int row = on ? (int)(gid / tpr) : 0;
+    const int c8 = on ? (int)(gid % tpr) : 0;
+    const bool second = row >= rows;
+    if (second) row -= rows;
+    const long src = (!second && src_row) ? __ldg(src_row + row) : row;
+    uint8_t* const qo = second ? q8b : q8;
+    uint8_t* const so = second ? sfb : sf;
     uint4 raw = make_uint4(0, 0, 0, 0);
     if (on) raw = __ldg(reinterpret_cast<const uint4*>(x + src * x_ld) + c8);
     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -565,8 +573,8 @@ __global__ void __launch_bounds__(256) mx_quantize_rows_vec_kernel(const __nv_bf
         }
         o[h] = w;
     }
-    *reinterpret_cast<uint2*>(q8 + (long)row * K + c8 * 8) = make_uint2(o[0], o[1]);
-    if ((c8 & 3) == 0) sf[(long)row * (K >> 5) + (c8 >> 2)] = (uint8_t)sb;
+    *reinterpret_cast<uint2*>(qo + (long)row * K + c8 * 8) = make_uint2(o[0], o[1]);
+    if ((c8 & 3) == 0) so[(long)row * (K >> 5) + (c8 >> 2)] = (uint8_t)sb;
 }
 
 // ------------------------------------------------------------------ host side
@@ -688,18 +696,26 @@ int mx_device_error(int* out, cudaStream_t stream) {
     return 0;
 }
 
-int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream) {
-    if (!x || !q8 || !sf || rows < 0 || K <= 0 || K % 32) return ERR_BAD_ARG;
-    if (rows == 0) return 0;
-    if (!((uintptr_t)x & 15) && x_ld % 8 == 0 && !((uintptr_t)q8 & 7)) {
-        const long threads = (long)rows * (K / 8);
-        mx_quantize_rows_vec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf);
+int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream, int rows2,
+                     uint8_t* q8b, uint8_t* sfb) {
+    if (!x || !q8 || !sf || rows < 0 || rows2 < 0 || K <= 0 || K % 32 || (rows2 > 0 && (!q8b || !sfb))) return ERR_BAD_ARG;
+    if (rows + rows2 == 0) return 0;
+    if (!((uintptr_t)x & 15) && x_ld % 8 == 0 && !((uintptr_t)q8 & 7) && !((uintptr_t)q8b & 7)) {
+        const long threads = (long)(rows + rows2) * (K / 8);
+        mx_quantize_rows_vec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf, rows2, q8b, sfb);
         B200_CHECK_LAUNCH();
         return 0;
     }
-    const long warps = (long)rows * (K / 32);
-    mx_quantize_rows_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf);
-    B200_CHECK_LAUNCH();
+    if (rows > 0) {
+        const long warps = (long)rows * (K / 32);
+        mx_quantize_rows_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf);
+        B200_CHECK_LAUNCH();
+    }
+    if (rows2 > 0) {
+        const long warps = (long)rows2 * (K / 32);
+        mx_quantize_rows_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, stream>>>(x, x_ld, nullptr, rows2, K, q8b, sfb);
+        B200_CHECK_LAUNCH();
+    }
     return 0;
 }
 

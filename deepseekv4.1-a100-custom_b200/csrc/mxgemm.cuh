@@ -69,6 +69,8 @@ int mx_device_error(int* out, cudaStream_t stream);  // copies and clears the de
 
 // bf16 [rows][K] -> e4m3 bytes + E8M0 scale byte per 32 (the FP8 fake quantisation of dsv41/quant.py:46-54 kept in
 // quantised form); optional row gather: output row p reads input row src_row[p]
-int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream);
+// a second row set (rows2 > 0): input rows 0 .. rows2-1, ungathered, into q8b / sfb in the same launch
+int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, cudaStream_t stream, int rows2 = 0,
+                     uint8_t* q8b = nullptr, uint8_t* sfb = nullptr);
 
 }  // namespace b200
