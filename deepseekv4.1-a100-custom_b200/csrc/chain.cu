@@ -373,10 +373,11 @@ extern "C" size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int in
 }
 
 extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
-    if (!m || !m->logits || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
+    if (!m) return ERR_BAD_ARG;
     if (m->tokens < 0 || m->topk < 1 || m->n_experts < 1 || m->dim < 1 || m->inter < 1) return ERR_BAD_ARG;
+    if (m->tokens == 0) return 0;  // an empty batch is not an error; its (empty) buffers may be null
+    if (!m->logits || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
     if (m->has_shared && (!m->sh_w13 || !m->sh_s13 || !m->sh_w2 || !m->sh_s2)) return ERR_BAD_ARG;
-    if (m->tokens == 0) return 0;
     const int T = m->tokens, topk = m->topk, D = m->dim, I = m->inter, E = m->n_experts;
     const long P = (long)T * topk;
     if (P > (1L << 30) || E > ROUTE_MAX_EXPERTS || topk > 32 || topk > E) return ERR_BAD_SHAPE;

@@ -145,3 +145,48 @@ def test_expert_parallel_layer_world_of_one_equals_layer(mods, dev):
         assert torch.equal(got, layer.forward(x, logits))
     finally:
         dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------ edge cases
+def test_layer_empty_batch(mods, dev):
+    _, _, layer = _layer(mods, dev, 8, 256, 128, 2, 51)
+    out = layer.forward(torch.empty(0, 256, dtype=torch.bfloat16, device=dev), torch.empty(0, 8, device=dev))
+    assert out.shape == (0, 256)
+
+
+def _skewed_logits(T, E, hot, topk):
+    # every token ranks the `hot` experts first, in the same order: the worst imbalance the router can produce
+    lg = torch.full((T, E), -30.0)
+    for r, e in enumerate(hot[:topk]):
+        lg[:, e] = 10.0 - r
+    return lg
+
+
+@pytest.mark.parametrize("T", [40, 128, 129, 300])
+@pytest.mark.parametrize("engine", [0, 1])
+def test_layer_all_tokens_on_the_same_experts(mods, oracle, dev, T, engine):
+    # groups larger than a work (32 tokens in decode, 128 in prefill), exactly one tile, one tile plus one token
+    if engine == 1 and T > 128:
+        pytest.skip("the streaming kernels serve decode-sized batches")
+    E, D, I, topk = 16, 512, 256, 2
+    ex, sh, layer = _layer(mods, dev, E, D, I, topk, 61, engine=engine)
+    x = mods.synth.make_tokens(T, D, 63)
+    logits = _skewed_logits(T, E, [5, 11], topk)
+    ref = oracle.moe_layer(x, logits, None, ex["w13"], ex["s13"], ex["w2"], ex["s2"], (sh["w13"], sh["s13"], sh["w2"], sh["s2"]), topk=topk, limit=10.0)
+    out, eid, wt = layer.forward(x.to(dev), logits.to(dev), want_route=True)
+    assert torch.equal(eid.cpu(), ref["eid"]) and set(eid.unique().tolist()) == {5, 11}
+    assert rel_err(out, ref["out"]) <= 1e-2
+    assert mods.cukern.device_error(dev) == 0
+
+
+def test_layer_largest_router(mods, oracle, dev):
+    # 1024 experts and 32 experts per token: the limits of the router and of the bucketing
+    E, D, I, topk, T = 1024, 256, 128, 32, 5
+    ex, sh, layer = _layer(mods, dev, E, D, I, topk, 71)
+    x = mods.synth.make_tokens(T, D, 73)
+    logits = mods.synth.make_logits(T, E, 74, topk=topk)
+    ref = oracle.moe_layer(x, logits.float(), None, ex["w13"], ex["s13"], ex["w2"], ex["s2"], (sh["w13"], sh["s13"], sh["w2"], sh["s2"]), topk=topk, limit=10.0)
+    out, eid, wt = layer.forward(x.to(dev), logits.to(dev), want_route=True)
+    assert torch.equal(eid.cpu(), ref["eid"])
+    assert torch.allclose(wt.cpu(), ref["wt"], rtol=2e-5, atol=1e-9)
+    assert rel_err(out, ref["out"]) <= 1e-2
