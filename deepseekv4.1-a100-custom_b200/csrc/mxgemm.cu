@@ -84,6 +84,11 @@ __device__ __forceinline__ uint32_t mx_idesc(int b_fmt, int n, int j) {
            ((uint32_t)j << 29);
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, int x, int y, int z, int w, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst), "l"(tm),
+                 "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(tm), "r"(x),
                  "r"(y), "r"(bar)
@@ -113,8 +118,8 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     const int n_sfb = (NW + 127) >> 7;             // scale atoms of the weight side
     const int n_atoms = 1 + n_sfb;
     uint8_t* base = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-    // stage layout: [kb] token boxes (nd x 128 B), then [kb] weight tiles (NW x 128 B; dual: gate box then up box)
-    const uint32_t x_box = (uint32_t)nd * 128u, w_half = (uint32_t)rows_w * 128u, w_tile = (uint32_t)NW * 128u;
+    // stage layout: [kb] token boxes (nd x 128 B), then [kb] weight tiles (NW x 128 B; dual: gate rows then up rows)
+    const uint32_t x_box = (uint32_t)nd * 128u, w_tile = (uint32_t)NW * 128u;
     const uint32_t stage_bytes = (uint32_t)KB * (x_box + w_tile);
     uint8_t* ring = base;
     uint8_t* sf_ring = base + (size_t)NS * stage_bytes;   // per stage: [kb][n_atoms] atoms of 512 B
@@ -218,8 +223,10 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                         for (int b = 0; b < nkb; ++b) {
                             const int kx = (kb0 + b) * 128;  // element coordinate along K (bytes for e4m3, 4-bit elements for E2M1)
                             const uint32_t wdst = dst + (uint32_t)KB * x_box + (uint32_t)b * w_tile;
-                            tma_load_3d(wdst, tw, kx, row0, c.w.x, bar_full_ab(s));
-                            if (a.dual) tma_load_3d(wdst + w_half, tw, kx, a.inter + row0, c.w.x, bar_full_ab(s));
+                            // dual: the weight map is 4-D {k, row within a half, half, expert}: one box fetches the gate rows and,
+                            // right behind them in shared memory, the up rows
+                            if (a.dual) tma_load_4d(wdst, tw, kx, row0, 0, c.w.x, bar_full_ab(s));
+                            else tma_load_3d(wdst, tw, kx, row0, c.w.x, bar_full_ab(s));
                             tma_load_2d(dst + (uint32_t)b * x_box, tx, kx, c.w.y, bar_full_ab(s));
                         }
                     }
@@ -584,7 +591,7 @@ static int make_tmap(CUtensorMap* tm, CUtensorMapDataType dt, int rank, const vo
                      const cuuint32_t* box) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return (int)cudaErrorNotSupported;
-    cuuint32_t estr[3] = {1, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(tm, dt, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
@@ -609,10 +616,20 @@ static int make_prob_tmaps(const MxArgs& a, const MxProb& p, CUtensorMap* tm_w, 
     const bool fp4 = p.a_fmt == MX_A_E2M1;
     const uint64_t row_bytes = fp4 ? (uint64_t)a.K / 2 : (uint64_t)a.K;
     const uint64_t experts = p.n_experts > 0 ? p.n_experts : 1;
-    cuuint64_t dims[3] = {(cuuint64_t)a.K, (cuuint64_t)p.N, experts};
-    cuuint64_t strides[2] = {row_bytes, (experts == 1 || p.w_estride == 0) ? row_bytes * (uint64_t)p.N : (cuuint64_t)p.w_estride};
-    cuuint32_t box[3] = {128, (cuuint32_t)a.rows_a, 1};
-    int rc = make_tmap(tm_w, fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, p.w, dims, strides, box);
+    const cuuint64_t estride = (experts == 1 || p.w_estride == 0) ? row_bytes * (uint64_t)p.N : (cuuint64_t)p.w_estride;
+    const CUtensorMapDataType dt = fp4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    int rc;
+    if (a.dual) {  // {k, row within a half, half (gate | up), expert}: a box of two halves is one instruction; rows past `inter` read as zero
+        cuuint64_t dims[4] = {(cuuint64_t)a.K, (cuuint64_t)a.inter, 2, experts};
+        cuuint64_t strides[3] = {row_bytes, row_bytes * (uint64_t)a.inter, estride};
+        cuuint32_t box[4] = {128, (cuuint32_t)a.rows_a, 2, 1};
+        rc = make_tmap(tm_w, dt, 4, p.w, dims, strides, box);
+    } else {
+        cuuint64_t dims[3] = {(cuuint64_t)a.K, (cuuint64_t)p.N, experts};
+        cuuint64_t strides[2] = {row_bytes, estride};
+        cuuint32_t box[3] = {128, (cuuint32_t)a.rows_a, 1};
+        rc = make_tmap(tm_w, dt, 3, p.w, dims, strides, box);
+    }
     if (rc) return rc;
     cuuint64_t xdims[2] = {(cuuint64_t)a.K, (cuuint64_t)(p.x8_rows > 0 ? p.x8_rows : 1)};
     cuuint64_t xstrides[1] = {(cuuint64_t)a.K};
