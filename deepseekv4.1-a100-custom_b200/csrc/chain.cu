@@ -1,7 +1,8 @@
-// MoE layer for a decode batch and the C-ABI entry points of the grouped FP4 / dense FP8 GEMMs.
+// MoE layer (any batch size) and the C-ABI entry points of the grouped FP4 / dense FP8 GEMMs.
 //
-// Layer = one routing kernel (input fake quantisation, router, bucketing of the (token, expert) pairs by expert,
-// work list) followed by the weight-streaming skinny GEMMs (skinny.cu) with fused epilogues and a final combine.
+// Layer = one routing kernel (router, bucketing of the (token, expert) pairs by expert, work list; for the streaming engine also
+// the input fake quantisation), then either the block-scaled tensor-core GEMMs (mxgemm.cu: one quantisation launch, gate/up GEMM and
+// down GEMM, each carrying the routed experts and the shared expert) or the weight-streaming GEMMs (skinny.cu), then a combine.
 #include "common.cuh"
 #include "skinny.cuh"
 #include "mxgemm.cuh"
@@ -413,7 +414,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
     r.x = (const __nv_bfloat16*)m->x; r.xq = (m->x_is_quantized || use_mx) ? nullptr : w.xq;
     r.shard_start = m->shard_start; r.shard_n = shard_n;
-    const int nd = small ? MX_ND_DECODE : 128;  // token columns per work of the tensor-core path
+    const int nd = small ? MX_ND_DECODE : 128;  // tokens per work of the tensor-core path
     r.tpw = use_mx ? nd : SK_TOK;
     r.eid = w.eid; r.wt = w.wt; r.pair_tok = w.pair_tok; r.pair_out = w.pair_out; r.pair_w = w.pair_w; r.work = w.work; r.n_work = w.n_work;
     r.counter = w.counter; r.no_bucket = small ? 0 : 1;

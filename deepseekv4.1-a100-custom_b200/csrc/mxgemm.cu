@@ -97,8 +97,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm,
 
 // ------------------------------------------------------------------ the kernel
 // Tile orientation: the tokens of a work are the M side of the tensor-core tile (128 accumulator lanes, of which the first
-// `ntok` carry data), the weight rows are the N side (up to 256 per MMA: the MMA time hardly depends on N, so every
-// instruction should carry as many weight bytes as possible).  D[token, weight row] lives in TMEM columns [0, N_w).
+// `ntok` carry data), the weight rows are the N side (up to 256 per MMA: the fixed cost per instruction and per pipeline stage is
+// what bounds the kernel, so every instruction carries as many weight bytes as possible).  D[token, weight row] lives in TMEM
+// columns [0, N_w).
 //   dual (SwiGLU epilogue): N_w = 2 * rows_w, columns [0, rows_w) = gate rows row0.., columns [rows_w, 2 rows_w) = up rows
 //   single:                 N_w = rows_w consecutive rows
 // One launch runs up to two problems that share K, the tile shape and the token count per work (the routed experts and the
