@@ -26,6 +26,7 @@ struct RouteArgs {
     int mode, norm;
     const __nv_bfloat16* x;
     __nv_bfloat16* xq;  // nullptr: x is already quantised
+    long long x_ld, logits_ld;  // row strides (elements) of x and of the logits
     int shard_start, shard_n;
     int tpw;            // pairs per work
     int* eid;           // [tokens, topk]
@@ -57,7 +58,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
     if (a.xq) {
         const int groups = a.dim >> 5;
         for (int gi = tid; gi < groups; gi += ROUTE_THREADS) {
-            const uint4* src = reinterpret_cast<const uint4*>(a.x + (long)tok * a.dim + gi * 32);
+            const uint4* src = reinterpret_cast<const uint4*>(a.x + (long)tok * a.x_ld + gi * 32);
             uint4 v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = src[j];
@@ -80,7 +81,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
         }
     }
     if (warp == 0)
-        gate_topk_warp(a.logits_f32 ? a.logits_f32 + (long)tok * a.E : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.E : nullptr, a.bias, a.E,
+        gate_topk_warp(a.logits_f32 ? a.logits_f32 + (long)tok * a.logits_ld : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E,
                        a.temp, a.topk, a.route_scale, a.mode, a.norm, a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
     if (a.no_bucket) return;
     __threadfence();
@@ -376,6 +377,7 @@ extern "C" size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int in
 extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (!m) return ERR_BAD_ARG;
     if (m->tokens < 0 || m->topk < 1 || m->n_experts < 1 || m->dim < 1 || m->inter < 1) return ERR_BAD_ARG;
+    if ((m->x_ld > 0 && m->x_ld < m->dim) || (m->logits_ld > 0 && m->logits_ld < m->n_experts)) return ERR_BAD_ARG;
     if (m->tokens == 0) return 0;  // an empty batch is not an error; its (empty) buffers may be null
     if (!m->logits || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
     if (m->has_shared && (!m->sh_w13 || !m->sh_s13 || !m->sh_w2 || !m->sh_s2)) return ERR_BAD_ARG;
@@ -413,6 +415,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
     r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
     r.x = (const __nv_bfloat16*)m->x; r.xq = (m->x_is_quantized || use_mx) ? nullptr : w.xq;
+    const long long x_ld = m->x_ld > 0 ? m->x_ld : D;  // rows of x / logits may sit inside wider rows (a packed exchange buffer)
+    r.x_ld = x_ld; r.logits_ld = m->logits_ld > 0 ? m->logits_ld : E;
     r.shard_start = m->shard_start; r.shard_n = shard_n;
     const int nd = small ? MX_ND_DECODE : 128;  // tokens per work of the tensor-core path
     r.tpw = use_mx ? nd : SK_TOK;
@@ -437,7 +441,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (use_mx) {
         // activations -> e4m3 + E8M0 (the FP8 fake quantisation kept in quantised form), gathered into pair-sorted order
         // (and, for the shared expert, in token order: one launch for both)
-        if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, D, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream, shared ? T : 0, w.x8t, w.xsft))) return rc;
+        if ((rc = mx_quantize_rows((const __nv_bfloat16*)m->x, x_ld, w.pair_tok, (int)P, D, w.x8s, w.xsfs, stream, shared ? T : 0, w.x8t, w.xsft))) return rc;
         // always the widest tiles (256 weight rows per MMA): even when that leaves fewer (work, tile) items than SMs, as for a single
         // token (6 works x 16 tiles), the wide tiles stream faster than more, narrower ones (measured 83 us against 136 us per step)
         const int rows1 = 128, rows2 = 256;
@@ -493,7 +497,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         SkinnyArgs a{};
         a.w = (const uint8_t*)m->w13; a.w_estride = (long long)2 * I * (D / 2); a.n_experts = shard_n;
         a.s = (const uint8_t*)m->s13; a.s_estride = (long long)2 * I * (D / 32) * sbytes; a.s_rstride = (D / 32) * sbytes;
-        a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = D;
+        const long long xin_ld = m->x_is_quantized ? x_ld : D;
+        a.N = 2 * I; a.K = D; a.x = xin; a.x_ld = xin_ld;
         a.work = w.work; a.n_work = w.n_work; a.pair_tok = w.pair_tok; a.pair_out = nullptr; a.pair_w = w.pair_w;
         a.out = w.hq; a.out_ld = I; a.limit = m->swiglu_limit; a.inter = I;
         if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
@@ -512,7 +517,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             SkinnyArgs c{};
             c.w = (const uint8_t*)m->sh_w13; c.s = (const uint8_t*)m->sh_s13;
             c.s_rstride = m->shared_fmt == SK_FMT_FP8_E8M0 ? m->sh_s13_cols : m->sh_s13_cols * 4;
-            c.N = 2 * I; c.K = D; c.x = xin; c.x_ld = D; c.w_permk = m->sh_permk;
+            c.N = 2 * I; c.K = D; c.x = xin; c.x_ld = xin_ld; c.w_permk = m->sh_permk;
             c.work = nullptr; c.dense_rows = T; c.n_work_host = (T + SK_TOK - 1) / SK_TOK;
             c.out = w.hs; c.out_ld = I; c.limit = m->swiglu_limit; c.inter = I; c.round_gu_bf16 = 1;
             if ((rc = skinny_launch(c, m->shared_fmt, SK_EPI_SWIGLU, stream))) return rc;

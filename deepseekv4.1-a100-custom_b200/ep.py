@@ -70,15 +70,28 @@ class EPMoE:
         assert counts[self.rank] == T_r
         T = sum(counts)
         even = all(c == counts[0] for c in counts)
-        # dispatch: all tokens to all ranks
-        x_all = torch.empty(T, x_local.shape[1], dtype=x_local.dtype, device=x_local.device)
-        l_all = torch.empty(T, logits_local.shape[1], dtype=logits_local.dtype, device=logits_local.device)
-        if even:
-            dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=self.group)
-            dist.all_gather_into_tensor(l_all, logits_local.contiguous(), group=self.group)
+        # dispatch: all tokens to all ranks.  With equal token counts the rows [x | logits] of this rank travel in ONE all-gather (the
+        # exchange is latency-bound: one collective less is worth more than the two small packing copies); the layer reads x and the
+        # logits as strided views of the gathered buffer.
+        D, E = x_local.shape[1], logits_local.shape[1]
+        xb, lb = D * x_local.element_size(), E * logits_local.element_size()
+        if even and W > 1 and x_local.is_cuda and xb % 16 == 0 and lb % 16 == 0:
+            mine = torch.empty(T_r, xb + lb, dtype=torch.uint8, device=x_local.device)
+            mine[:, :xb].view(x_local.dtype).copy_(x_local)
+            mine[:, xb:].view(logits_local.dtype).copy_(logits_local)
+            both = torch.empty(T, xb + lb, dtype=torch.uint8, device=x_local.device)
+            dist.all_gather_into_tensor(both, mine, group=self.group)
+            x_all = both[:, :xb].view(x_local.dtype)
+            l_all = both[:, xb:].view(logits_local.dtype)
         else:
-            dist.all_gather(list(x_all.split(counts)), x_local.contiguous(), group=self.group)
-            dist.all_gather(list(l_all.split(counts)), logits_local.contiguous(), group=self.group)
+            x_all = torch.empty(T, D, dtype=x_local.dtype, device=x_local.device)
+            l_all = torch.empty(T, E, dtype=logits_local.dtype, device=logits_local.device)
+            if even:
+                dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=self.group)
+                dist.all_gather_into_tensor(l_all, logits_local.contiguous(), group=self.group)
+            else:
+                dist.all_gather(list(x_all.split(counts)), x_local.contiguous(), group=self.group)
+                dist.all_gather(list(l_all.split(counts)), logits_local.contiguous(), group=self.group)
         fused = self.layer is not None and self.partial_fn == self._partial_cuda and self.shared_fn == self._shared_cuda
         if fused:
             # local experts over all tokens; the shared expert rides in the same launches (its weight stream costs the same for all

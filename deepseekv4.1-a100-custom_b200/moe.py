@@ -82,9 +82,11 @@ class MoELayer:
         Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
         and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel."""
         dev = L.require_cuda(x, logits, out)
-        assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.is_contiguous()
+        # rows may be strided (views into a wider buffer), the elements of a row are contiguous
+        assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.stride(1) == 1
+        assert (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0
         T = x.shape[0]
-        assert logits.shape == (T, self.n_experts) and logits.dtype in (torch.float32, torch.bfloat16) and logits.is_contiguous()
+        assert logits.shape == (T, self.n_experts) and logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(1) == 1
         lib = L.lib()
         mx = self._use_mx(T)
         if final and out is None:
@@ -101,6 +103,7 @@ class MoELayer:
         a.temp, a.route_scale = float(self.gate_temp), float(self.route_scale)
         a.score_mode, a.norm = L.SCORE_MODES[self.score_func], int(self.norm)
         a.x, a.x_is_quantized = x.data_ptr(), int(x_is_quantized)
+        a.x_ld, a.logits_ld = (x.stride(0) if T > 1 else self.dim), (logits.stride(0) if T > 1 else self.n_experts)
         a.w13, a.s13, a.w2, a.s2 = self.w13.data_ptr(), self.s13.data_ptr(), self.w2.data_ptr(), self.s2.data_ptr()
         a.expert_fmt, a.shard_start, a.shard_n = self.expert_fmt, self.shard_start, self.n_local
         shared = with_shared and self.sh_w13 is not None and (final or want_shared)

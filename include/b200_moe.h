@@ -168,6 +168,9 @@ typedef struct b200_moe_args {
     /* optional: the shared expert's own result, bf16 [tokens, dim] (NULL = not wanted).  With has_shared it is computed even when
      * `out` is NULL; an expert-parallel caller adds it to the routed sum it gets back from the exchange. */
     void* shared_out;
+    /* row strides, in elements, of x and of the logits; 0 = dense (dim / n_experts).  Lets both live inside wider rows, e.g. the
+     * rows [x | logits] of one exchange buffer.  x rows must stay 16-byte aligned. */
+    long long x_ld, logits_ld;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);

@@ -190,3 +190,19 @@ def test_layer_largest_router(mods, oracle, dev):
     assert torch.equal(eid.cpu(), ref["eid"])
     assert torch.allclose(wt.cpu(), ref["wt"], rtol=2e-5, atol=1e-9)
     assert rel_err(out, ref["out"]) <= 1e-2
+
+
+@pytest.mark.parametrize("engine,T", [(1, 6), (2, 6), (0, 150)])
+def test_layer_reads_strided_rows(mods, dev, engine, T):
+    # x and the logits as views into wider rows [x | logits], the layout of the packed expert-parallel exchange buffer
+    E, D, I, topk = 16, 512, 256, 4
+    _, _, layer = _layer(mods, dev, E, D, I, topk, 81, engine=engine)
+    x = mods.synth.make_tokens(T, D, 83).to(dev)
+    logits = mods.synth.make_logits(T, E, 84, topk=topk).to(dev).float()
+    both = torch.zeros(T, D * 2 + E * 4, dtype=torch.uint8, device=dev)
+    both[:, :D * 2].view(torch.bfloat16).copy_(x)
+    both[:, D * 2:].view(torch.float32).copy_(logits)
+    xv, lv = both[:, :D * 2].view(torch.bfloat16), both[:, D * 2:].view(torch.float32)
+    assert not xv.is_contiguous() and xv.stride(0) == (D * 2 + E * 4) // 2
+    assert torch.equal(layer.forward(xv, lv), layer.forward(x, logits))
+    assert mods.cukern.device_error(dev) == 0

@@ -34,7 +34,7 @@ def test_moe_args_struct_matches_header(mods):
         stmt = stmt.strip()
         if not stmt:
             continue
-        decl = re.sub(r"^(const\s+)?(void|float|int|size_t)\s*\*?\s*", "", stmt)
+        decl = re.sub(r"^(const\s+)?(void|float|int|size_t|long long)\s*\*?\s*", "", stmt)
         names += [n.strip().lstrip("*").strip() for n in decl.split(",")]
     assert names == [f[0] for f in mods.lib.MoeArgs._fields_]
 
