@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
     __shared__ int s_cur[ROUTE_MAX_EXPERTS];
     __shared__ int s_wtot[2][ROUTE_THREADS / 32];
     const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();  // the next kernel may be placed early; it waits for this one to complete before it reads anything
 
     if (a.xq) {
         const int groups = a.dim >> 5;
@@ -208,6 +209,7 @@ __global__ void pair_scatter_kernel(const int* __restrict__ eid, const float* __
 
 // out[t, n] = bf16(acc[t, n] + float(ys[t, n]))
 __global__ void moe_finalize_kernel(const float* __restrict__ acc, const __nv_bfloat16* __restrict__ ys, __nv_bfloat16* __restrict__ out, long n) {
+    pdl_wait();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2bfloat16_rn(acc[i] + (ys ? __bfloat162float(ys[i]) : 0.f));
 }
@@ -217,6 +219,7 @@ __global__ void moe_finalize_kernel(const float* __restrict__ acc, const __nv_bf
 __global__ void moe_combine_kernel(const float* __restrict__ y2, const int* __restrict__ eid, const __nv_bfloat16* __restrict__ ys,
                                    __nv_bfloat16* __restrict__ out, float* __restrict__ routed, int tokens, int topk, int dim, int shard_start,
                                    int shard_n) {
+    pdl_wait();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long)tokens * dim) return;
     const int t = (int)(i / dim), n = (int)(i % dim);
@@ -533,13 +536,15 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     // ---- combine: routed sum (+ shared expert) -> bf16
     const long n = (long)T * D;
     if (small) {
-        moe_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.y2, w.eid, shared ? ys_buf : nullptr, (__nv_bfloat16*)m->out, m->routed_out, T, topk, D,
-                                                                           m->shard_start, shard_n);
-        B200_CHECK_LAUNCH();
+        if ((ce = launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.y2, (const int*)w.eid,
+                             (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, m->routed_out, T, topk, D, m->shard_start, shard_n)) !=
+            cudaSuccess)
+            return (int)ce;
     } else {
         if (m->out) {
-            moe_finalize_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w.acc, shared ? ys_buf : nullptr, (__nv_bfloat16*)m->out, n);
-            B200_CHECK_LAUNCH();
+            if ((ce = launch_pdl(moe_finalize_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.acc,
+                                 (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, n)) != cudaSuccess)
+                return (int)ce;
         }
         if (m->routed_out && (ce = cudaMemcpyAsync(m->routed_out, w.acc, sizeof(float) * n, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
     }

@@ -24,6 +24,30 @@ enum : int {
         if (e__ != cudaSuccess) return (int)e__;     \
     } while (0)
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// The kernels of a layer step are launched with the programmatic-serialisation attribute: a kernel may be placed on SMs that the
+// kernel before it in the stream has already left and run its prologue there (barrier set-up, TMEM allocation, descriptor fetch)
+// instead of waiting for the whole grid to drain.  pdl_wait() blocks until the preceding kernel has completed and its writes
+// are visible; every kernel launched this way calls it before it touches global memory, so the usual stream order holds for data.
+// Launched without the attribute both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ------------------------------------------------------------------ bit casts / bf16
 __device__ __forceinline__ float u32_as_f32(uint32_t u) { return __uint_as_float(u); }
 __device__ __forceinline__ uint32_t f32_as_u32(float f) { return __float_as_uint(f); }

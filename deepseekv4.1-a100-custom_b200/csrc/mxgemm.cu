@@ -132,18 +132,6 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     auto bar_acc_full = [&](int b) { return smem_u32(&bars[3 * MX_MAX_STAGES + b]); };
     auto bar_acc_empty = [&](int b) { return smem_u32(&bars[3 * MX_MAX_STAGES + 2 + b]); };
 
-    const int kblocks = a.K >> 7;                       // 128-wide k blocks
-    const int spi = (kblocks + KB - 1) / KB;            // stages per item
-    // items per work and items in all of each problem
-    const int ipw0 = ((a.dual ? a.inter : a.p[0].N) + rows_w - 1) / rows_w;
-    const int ipw1 = a.n_prob > 1 ? ((a.dual ? a.inter : a.p[1].N) + rows_w - 1) / rows_w : 1;
-    const long items0 = (long)(a.p[0].n_work ? *a.p[0].n_work : a.p[0].n_work_host) * ipw0;
-    const long items1 = a.n_prob > 1 ? (long)(a.p[1].n_work ? *a.p[1].n_work : a.p[1].n_work_host) * ipw1 : 0;
-    const long total = items0 + items1;
-    const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
-    const int n_acc = (2 * NW <= MX_ACC_COLS_MAX) ? 2 : 1;  // two accumulator buffers (epilogue overlaps the next item) when they fit
-    const uint32_t sf_col0 = (uint32_t)(n_acc * NW);        // the scale columns follow the accumulators
-
     if (tid == 0) {
         abort_flag = 0;
         for (int s = 0; s < NS; ++s) {
@@ -165,6 +153,21 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sh;
+    // everything above touched no global memory: from here on the kernel before this one in the stream must have completed
+    pdl_wait();
+    pdl_launch_dependents();
+    const int kblocks = a.K >> 7;                       // 128-wide k blocks
+    const int spi = (kblocks + KB - 1) / KB;            // stages per item
+    // items per work and items in all of each problem
+    const int ipw0 = ((a.dual ? a.inter : a.p[0].N) + rows_w - 1) / rows_w;
+    const int ipw1 = a.n_prob > 1 ? ((a.dual ? a.inter : a.p[1].N) + rows_w - 1) / rows_w : 1;
+    const long items0 = (long)(a.p[0].n_work ? *a.p[0].n_work : a.p[0].n_work_host) * ipw0;
+    const long items1 = a.n_prob > 1 ? (long)(a.p[1].n_work ? *a.p[1].n_work : a.p[1].n_work_host) * ipw1 : 0;
+    const long total = items0 + items1;
+    const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
+    const int n_acc = (2 * NW <= MX_ACC_COLS_MAX) ? 2 : 1;  // two accumulator buffers (epilogue overlaps the next item) when they fit
+    const uint32_t sf_col0 = (uint32_t)(n_acc * NW);        // the scale columns follow the accumulators
+
 
     // position in the flat item list: problem, work, tile of the work; `w` = {local expert, first token row, tokens, -}
     struct ItemCur { long item; int pr, wk, it; int4 w; };
@@ -544,6 +547,8 @@ __global__ void mx_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, lon
 __global__ void __launch_bounds__(256) mx_quantize_rows_vec_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const int* __restrict__ src_row,
                                                                    int rows, int K, uint8_t* __restrict__ q8, uint8_t* __restrict__ sf, int rows2,
                                                                    uint8_t* __restrict__ q8b, uint8_t* __restrict__ sfb) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int tpr = K >> 3;  // threads per row
     const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
     const bool on = gid < (long)(rows + rows2) * tpr;  // K % 32 == 0: the 4 threads of a group are on or off together
@@ -695,9 +700,8 @@ int mx_launch(const MxArgs& a_in, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    mx_gemm_kernel<<<sm_count(), MX_THREADS, smem, stream>>>(a, tm[0], tm[1], tm[2], tm[3]);
-    B200_CHECK_LAUNCH();
-    return 0;
+    const cudaError_t le = launch_pdl(mx_gemm_kernel, dim3(sm_count()), dim3(MX_THREADS), smem, stream, a, tm[0], tm[1], tm[2], tm[3]);
+    return le == cudaSuccess ? 0 : (int)le;
 }
 
 int mx_device_error(int* out, cudaStream_t stream) {
@@ -720,9 +724,9 @@ int mx_quantize_rows(const __nv_bfloat16* x, long long x_ld, const int* src_row,
     if (rows + rows2 == 0) return 0;
     if (!((uintptr_t)x & 15) && x_ld % 8 == 0 && !((uintptr_t)q8 & 7) && !((uintptr_t)q8b & 7)) {
         const long threads = (long)(rows + rows2) * (K / 8);
-        mx_quantize_rows_vec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf, rows2, q8b, sfb);
-        B200_CHECK_LAUNCH();
-        return 0;
+        const cudaError_t le = launch_pdl(mx_quantize_rows_vec_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream, x, x_ld, src_row, rows, K, q8, sf,
+                                          rows2, q8b, sfb);
+        return le == cudaSuccess ? 0 : (int)le;
     }
     if (rows > 0) {
         const long warps = (long)rows * (K / 32);
