@@ -43,6 +43,7 @@ class MoELayer:
         if engine == 2 and not self._mx_ok:
             raise ValueError("engine 2 needs E8M0 scales for the experts and the shared expert and dims that are multiples of 128")
         self._sh_nat = None
+        self._args: dict = {}  # (tokens, engine) -> (argument block, workspace bytes), see forward
         if self._mx_ok and engine != 1 and sh_w13 is not None:
             from .w8 import unpermute_k
             self._sh_nat = (unpermute_k(sh_w13.w8), unpermute_k(sh_w2.w8))
@@ -94,36 +95,45 @@ class MoELayer:
         routed = torch.empty(T, self.dim, device=dev, dtype=torch.float32) if want_routed else None
         eid = torch.empty(T, self.topk, device=dev, dtype=torch.int32) if want_route else None
         wt = torch.empty(T, self.topk, device=dev, dtype=torch.float32) if want_route else None
-        nbytes = lib.b200_moe_workspace_bytes(T, self.topk, self.dim, self.inter)
-        ws = L.workspace(dev, nbytes, "moe")
-        a = L.MoeArgs()
-        a.tokens, a.n_experts, a.topk, a.dim, a.inter = T, self.n_experts, self.topk, self.dim, self.inter
-        a.logits, a.logits_is_bf16 = logits.data_ptr(), int(logits.dtype == torch.bfloat16)
-        a.gate_bias = self.gate_bias.data_ptr() if self.gate_bias is not None else None
-        a.temp, a.route_scale = float(self.gate_temp), float(self.route_scale)
-        a.score_mode, a.norm = L.SCORE_MODES[self.score_func], int(self.norm)
-        a.x, a.x_is_quantized = x.data_ptr(), int(x_is_quantized)
-        a.x_ld, a.logits_ld = (x.stride(0) if T > 1 else self.dim), (logits.stride(0) if T > 1 else self.n_experts)
-        a.w13, a.s13, a.w2, a.s2 = self.w13.data_ptr(), self.s13.data_ptr(), self.w2.data_ptr(), self.s2.data_ptr()
-        a.expert_fmt, a.shard_start, a.shard_n = self.expert_fmt, self.shard_start, self.n_local
         shared = with_shared and self.sh_w13 is not None and (final or want_shared)
         ys = torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16) if (want_shared and shared) else None
+        # the argument block is kept per (token count, engine): a decode loop calls this tens of thousands of times per second, so
+        # everything that does not change from call to call (weights, formats, router settings, workspace) is filled in once
+        key = (T, mx)
+        cached = self._args.get(key)
+        if cached is None:
+            a = L.MoeArgs()
+            a.tokens, a.n_experts, a.topk, a.dim, a.inter = T, self.n_experts, self.topk, self.dim, self.inter
+            a.gate_bias = self.gate_bias.data_ptr() if self.gate_bias is not None else None
+            a.temp, a.route_scale = float(self.gate_temp), float(self.route_scale)
+            a.score_mode, a.norm = L.SCORE_MODES[self.score_func], int(self.norm)
+            a.w13, a.s13, a.w2, a.s2 = self.w13.data_ptr(), self.s13.data_ptr(), self.w2.data_ptr(), self.s2.data_ptr()
+            a.expert_fmt, a.shard_start, a.shard_n = self.expert_fmt, self.shard_start, self.n_local
+            if self.sh_w13 is not None:
+                w13b, w2b = (self._sh_nat if mx else (self.sh_w13.w8, self.sh_w2.w8))
+                a.sh_w13, a.sh_s13, a.sh_w2, a.sh_s2 = w13b.data_ptr(), self.sh_w13.s8.data_ptr(), w2b.data_ptr(), self.sh_w2.s8.data_ptr()
+                a.shared_fmt = L.FMT_FP8_E8M0 if self.sh_w13.s8.dtype == torch.uint8 else L.FMT_FP8_F32B
+                a.sh_s13_cols, a.sh_s2_cols, a.sh_permk = self.sh_w13.s8.shape[1], self.sh_w2.s8.shape[1], int(not mx)
+            a.swiglu_limit = float(self.swiglu_limit)
+            a.engine = 2 if mx else 1
+            nbytes = lib.b200_moe_workspace_bytes(T, self.topk, self.dim, self.inter)
+            cached = self._args[key] = (a, nbytes)
+        a, nbytes = cached
+        ws = L.workspace(dev, nbytes, "moe")
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        a.logits, a.logits_is_bf16 = logits.data_ptr(), int(logits.dtype == torch.bfloat16)
+        a.x, a.x_is_quantized = x.data_ptr(), int(x_is_quantized)
+        a.x_ld, a.logits_ld = (x.stride(0) if T > 1 else self.dim), (logits.stride(0) if T > 1 else self.n_experts)
         a.has_shared = int(shared)
-        if shared:
-            w13b, w2b = (self._sh_nat if mx else (self.sh_w13.w8, self.sh_w2.w8))
-            a.sh_w13, a.sh_s13, a.sh_w2, a.sh_s2 = w13b.data_ptr(), self.sh_w13.s8.data_ptr(), w2b.data_ptr(), self.sh_w2.s8.data_ptr()
-            a.shared_fmt = L.FMT_FP8_E8M0 if self.sh_w13.s8.dtype == torch.uint8 else L.FMT_FP8_F32B
-            a.sh_s13_cols, a.sh_s2_cols, a.sh_permk = self.sh_w13.s8.shape[1], self.sh_w2.s8.shape[1], int(not mx)
-        a.swiglu_limit = float(self.swiglu_limit)
         a.out = out.data_ptr() if final else None
         a.routed_out = routed.data_ptr() if routed is not None else None
         a.shared_out = ys.data_ptr() if ys is not None else None
         a.eid_out = eid.data_ptr() if eid is not None else None
         a.wt_out = wt.data_ptr() if wt is not None else None
-        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        a.engine = 2 if mx else 1
         if prof_events is not None:  # (start, stop) torch.cuda.Event pair, already created (recorded once), timing enabled
             a.prof_start, a.prof_stop = prof_events[0].cuda_event, prof_events[1].cuda_event
+        else:
+            a.prof_start = a.prof_stop = None
         with torch.cuda.device(dev):
             L.check(lib.b200_moe_forward(ctypes.byref(a), L.stream_of(dev)), "b200_moe_forward")
         res = [out] if final else []
