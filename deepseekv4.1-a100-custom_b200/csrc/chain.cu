@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "skinny.cuh"
 #include "mxgemm.cuh"
+#include "gate_gemm.cuh"
 #include "router.cuh"
 #include "b200_moe.h"
 
@@ -27,6 +28,8 @@ struct RouteArgs {
     const __nv_bfloat16* x;
     __nv_bfloat16* xq;  // nullptr: x is already quantised
     long long x_ld, logits_ld;  // row strides (elements) of x and of the logits
+    int logit_parts;            // > 0: logits_f32 holds that many partial-sum slabs [tokens, E], logit_part_stride floats apart
+    long long logit_part_stride;
     int shard_start, shard_n;
     int tpw;            // pairs per work
     int* eid;           // [tokens, topk]
@@ -46,6 +49,7 @@ struct RouteArgs {
 // the shard's experts.
 __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArgs a) {
     __shared__ float s_val[ROUTE_MAX_EXPERTS], s_key[ROUTE_MAX_EXPERTS];  // router scratch of warp 0
+    __shared__ float s_raw[ROUTE_MAX_EXPERTS];                            // logits of the token when they arrive as k-split partial sums
     __shared__ int is_last;
     __shared__ int s_eid[ROUTE_MAX_PAIRS];
     __shared__ int s_cnt[ROUTE_MAX_EXPERTS];
@@ -81,9 +85,22 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
             for (int j = 0; j < 4; ++j) dst[j] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
     }
-    if (warp == 0)
-        gate_topk_warp(a.logits_f32 ? a.logits_f32 + (long)tok * a.logits_ld : nullptr, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E,
-                       a.temp, a.topk, a.route_scale, a.mode, a.norm, a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
+    if (a.logit_parts > 0) {
+        // the fused router projection leaves k-split partial sums: the whole block adds them, in split order, before warp 0 routes
+        const float* base = a.logits_f32 + (long)tok * a.E;
+        for (int e = tid; e < a.E; e += ROUTE_THREADS) {
+            float v = 0.f;
+#pragma unroll 4
+            for (int p = 0; p < a.logit_parts; ++p) v += __ldg(base + (long long)p * a.logit_part_stride + e);
+            s_raw[e] = v;
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        const float* row_f32 = a.logit_parts > 0 ? s_raw : (a.logits_f32 ? a.logits_f32 + (long)tok * a.logits_ld : nullptr);
+        gate_topk_warp(row_f32, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E, a.temp, a.topk, a.route_scale, a.mode, a.norm,
+                       a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
+    }
     if (a.no_bucket) return;
     __threadfence();
     __syncthreads();
@@ -336,6 +353,7 @@ struct MoeWs {
     __nv_bfloat16* xq; int* eid; float* wt; int* pair_tok; int* pair_out; float* pair_w; int4* work; int* n_work; unsigned int* counter;
     int* cnt; int* cursor; __nv_bfloat16* hq; __nv_bfloat16* hs; float* y2; float* acc; __nv_bfloat16* ys;
     uint8_t *x8s, *xsfs, *x8t, *xsft, *hq8, *hsf, *hs8, *hssf;
+    float* logit_parts;  // k-split partial logits of the fused router projection: [GATE_MAX_SPLITS or fewer][T][E]
 };
 
 static bool carve_moe(Carver& cv, MoeWs& w, int T, int topk, int D, int I) {
@@ -366,6 +384,12 @@ static bool carve_moe(Carver& cv, MoeWs& w, int T, int topk, int D, int I) {
     w.hsf = cv.take<uint8_t>((P + 128) * (I / 32));
     w.hs8 = cv.take<uint8_t>(((size_t)T + 128) * I);
     w.hssf = cv.take<uint8_t>(((size_t)T + 128) * (I / 32));
+    size_t lp = 0;  // the fused router projection: room for any expert count up to the router's maximum
+    for (int e = 64; e <= ROUTE_MAX_EXPERTS; e += 64) {
+        const size_t need = (size_t)gate_gemm_splits(T, e, D) * T * e;
+        if (need > lp) lp = need;
+    }
+    w.logit_parts = cv.take<float>(lp);
     return cv.ok;
 }
 
@@ -382,7 +406,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->tokens < 0 || m->topk < 1 || m->n_experts < 1 || m->dim < 1 || m->inter < 1) return ERR_BAD_ARG;
     if ((m->x_ld > 0 && m->x_ld < m->dim) || (m->logits_ld > 0 && m->logits_ld < m->n_experts)) return ERR_BAD_ARG;
     if (m->tokens == 0) return 0;  // an empty batch is not an error; its (empty) buffers may be null
-    if (!m->logits || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
+    if ((!m->logits && !m->gate_w) || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
     if (m->has_shared && (!m->sh_w13 || !m->sh_s13 || !m->sh_w2 || !m->sh_s2)) return ERR_BAD_ARG;
     const int T = m->tokens, topk = m->topk, D = m->dim, I = m->inter, E = m->n_experts;
     const long P = (long)T * topk;
@@ -416,10 +440,20 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     r.tokens = T; r.E = E; r.topk = topk; r.dim = D;
     r.logits_f32 = m->logits_is_bf16 ? nullptr : (const float*)m->logits;
     r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
+    if (!m->logits) {
+        // the path starts from the hidden state: router projection x @ gate_w^T in fp32 (dsv41/model.py:1615), left as k-split
+        // partial sums that the router adds in order
+        const int splits = gate_gemm_splits(T, E, D);
+        if ((rc = gate_gemm((const float*)m->xf, m->xf_ld > 0 ? m->xf_ld : D, m->xf ? nullptr : (const __nv_bfloat16*)m->x, m->x_ld > 0 ? m->x_ld : D,
+                            (const float*)m->gate_w, T, E, D, splits, w.logit_parts, stream)))
+            return rc;
+        r.logits_f32 = w.logit_parts; r.logits_bf16 = nullptr;
+        r.logit_parts = splits; r.logit_part_stride = (long long)T * E;
+    }
     r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
     r.x = (const __nv_bfloat16*)m->x; r.xq = (m->x_is_quantized || use_mx) ? nullptr : w.xq;
     const long long x_ld = m->x_ld > 0 ? m->x_ld : D;  // rows of x / logits may sit inside wider rows (a packed exchange buffer)
-    r.x_ld = x_ld; r.logits_ld = m->logits_ld > 0 ? m->logits_ld : E;
+    r.x_ld = x_ld; r.logits_ld = (m->logits && m->logits_ld > 0) ? m->logits_ld : E;
     r.shard_start = m->shard_start; r.shard_n = shard_n;
     const int nd = small ? MX_ND_DECODE : 128;  // tokens per work of the tensor-core path
     r.tpw = use_mx ? nd : SK_TOK;

@@ -18,7 +18,8 @@ __device__ inline void gate_topk_warp(const float* __restrict__ srow, const __nv
     const int lane = threadIdx.x & 31;
     float mx = -INFINITY;
     for (int e = lane; e < E; e += 32) {
-        const float v = __fdiv_rn(srow ? srow[e] : __bfloat162float(srow_bf16[e]), temp);
+        const float raw = srow ? srow[e] : __bfloat162float(srow_bf16[e]);
+        const float v = __fdiv_rn(raw, temp);
         s_val[e] = v;
         mx = fmaxf(mx, v);
     }

@@ -16,7 +16,7 @@ class MoELayer:
     def __init__(self, w13: torch.Tensor, s13: torch.Tensor, w2: torch.Tensor, s2: torch.Tensor, *, n_experts: int | None = None, topk: int = 6,
                  sh_w13: W8 | None = None, sh_w2: W8 | None = None, gate_bias: torch.Tensor | None = None, gate_temp: float = 1.0,
                  route_scale: float = 1.0, score_func: str = "softmax", norm_topk_prob: bool = True, swiglu_limit: float = 10.0,
-                 shard_start: int = 0, engine: int = 0):
+                 shard_start: int = 0, engine: int = 0, gate_w: torch.Tensor | None = None):
         """w13 uint8 [n, 2I, D/2], s13 [n, 2I, D/32] (uint8 E8M0 or bf16), w2 uint8 [n, D, I/2], s2 [n, D, I/32]: the n experts
         [shard_start, shard_start + n) of a layer with n_experts experts (shard dict of dsv41/load.py:213-232)."""
         dev = L.require_cuda(w13, s13, w2, s2, gate_bias)
@@ -35,6 +35,11 @@ class MoELayer:
         self.topk, self.gate_bias, self.gate_temp, self.route_scale = topk, gate_bias, gate_temp, route_scale
         self.score_func, self.norm, self.swiglu_limit = score_func, norm_topk_prob and topk > 1, swiglu_limit
         self.device = dev
+        # optional router matrix fp32 [n_experts, dim] (dsv41/model.py:1603): with it forward() can start from the hidden state
+        self.gate_w = None
+        if gate_w is not None:
+            assert gate_w.shape == (self.n_experts, self.dim) and gate_w.dtype == torch.float32 and gate_w.is_cuda
+            self.gate_w = gate_w.contiguous()
         # engine 0 = automatic (block-scaled tensor cores whenever the formats allow, else weight streaming), 1 = weight streaming with
         # in-register dequantisation, 2 = block-scaled tensor cores.  The tensor-core path reads the shared expert in natural k
         # order, so a natural-order copy is kept next to the W8 container.
@@ -77,9 +82,11 @@ class MoELayer:
         hs = swiglu_quant(linear_w(fake_quant_fp8(x, 32), self.sh_w13), None, self.inter, self.swiglu_limit)
         return linear_w(hs, self.sh_w2)
 
-    def forward(self, x: torch.Tensor, logits: torch.Tensor, *, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
+    def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None, *, xf: torch.Tensor | None = None, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
                 x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, want_shared: bool = False, prof_events=None):
-        """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E].
+        """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E]; logits=None (the layer was
+        built with gate_w): the router projection xf @ gate_w^T runs inside the call, xf fp32 [T, D] or None for x.float()
+        (dsv41/decode.py:449, dsv41/model.py:1615).
         Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
         and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel."""
         dev = L.require_cuda(x, logits, out)
@@ -87,7 +94,11 @@ class MoELayer:
         assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.stride(1) == 1
         assert (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0
         T = x.shape[0]
-        assert logits.shape == (T, self.n_experts) and logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(1) == 1
+        if logits is None:
+            assert self.gate_w is not None, "forward() without logits needs the layer's gate_w"
+            assert xf is None or (xf.shape == (T, self.dim) and xf.dtype == torch.float32 and xf.stride(1) == 1 and xf.is_cuda)
+        else:
+            assert logits.shape == (T, self.n_experts) and logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(1) == 1
         lib = L.lib()
         mx = self._use_mx(T)
         if final and out is None:
@@ -116,14 +127,18 @@ class MoELayer:
                 a.sh_s13_cols, a.sh_s2_cols, a.sh_permk = self.sh_w13.s8.shape[1], self.sh_w2.s8.shape[1], int(not mx)
             a.swiglu_limit = float(self.swiglu_limit)
             a.engine = 2 if mx else 1
+            a.gate_w = self.gate_w.data_ptr() if self.gate_w is not None else None
             nbytes = lib.b200_moe_workspace_bytes(T, self.topk, self.dim, self.inter)
             cached = self._args[key] = (a, nbytes)
         a, nbytes = cached
         ws = L.workspace(dev, nbytes, "moe")
         a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        a.logits, a.logits_is_bf16 = logits.data_ptr(), int(logits.dtype == torch.bfloat16)
+        a.logits = logits.data_ptr() if logits is not None else None
+        a.logits_is_bf16 = int(logits is not None and logits.dtype == torch.bfloat16)
+        a.xf, a.xf_ld = (xf.data_ptr(), xf.stride(0) if T > 1 else self.dim) if (logits is None and xf is not None) else (None, 0)
         a.x, a.x_is_quantized = x.data_ptr(), int(x_is_quantized)
-        a.x_ld, a.logits_ld = (x.stride(0) if T > 1 else self.dim), (logits.stride(0) if T > 1 else self.n_experts)
+        a.x_ld = x.stride(0) if T > 1 else self.dim
+        a.logits_ld = logits.stride(0) if (logits is not None and T > 1) else self.n_experts
         a.has_shared = int(shared)
         a.out = out.data_ptr() if final else None
         a.routed_out = routed.data_ptr() if routed is not None else None

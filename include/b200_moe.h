@@ -131,7 +131,7 @@ int b200_fp8_gemm(const void* x, long long x_ld, int M, const void* w8, const vo
  * cukern.expert_chain (dsv41/cukern.py:504-547); with a shard it is EPRuntime._experts_shard (dsv41/ep.py:324-338). */
 typedef struct b200_moe_args {
     int tokens, n_experts, topk, dim, inter;
-    /* router: logits [tokens, n_experts] fp32 (logits_is_bf16 = 0) or bf16; bias fp32 [n_experts] or NULL */
+    /* router: logits [tokens, n_experts] fp32 (logits_is_bf16 = 0) or bf16 (or NULL with gate_w, see below); bias fp32 [n_experts] or NULL */
     const void* logits;
     int logits_is_bf16;
     const float* gate_bias;
@@ -171,6 +171,12 @@ typedef struct b200_moe_args {
     /* row strides, in elements, of x and of the logits; 0 = dense (dim / n_experts).  Lets both live inside wider rows, e.g. the
      * rows [x | logits] of one exchange buffer.  x rows must stay 16-byte aligned. */
     long long x_ld, logits_ld;
+    /* optional router projection, so that the layer starts from the hidden state instead of from logits (dsv41/model.py:1615,
+     * dsv41/decode.py:449): with logits == NULL the layer computes logits = xf @ gate_w^T in fp32; gate_w fp32 [n_experts, dim];
+     * xf fp32 [tokens, dim] with row stride xf_ld (0 = dim), or NULL to use x converted to fp32. */
+    const void* gate_w;
+    const void* xf;
+    long long xf_ld;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);

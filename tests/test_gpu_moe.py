@@ -206,3 +206,27 @@ def test_layer_reads_strided_rows(mods, dev, engine, T):
     assert not xv.is_contiguous() and xv.stride(0) == (D * 2 + E * 4) // 2
     assert torch.equal(layer.forward(xv, lv), layer.forward(x, logits))
     assert mods.cukern.device_error(dev) == 0
+
+
+@pytest.mark.parametrize("T,use_xf", [(1, False), (5, True), (64, False), (200, True)])
+def test_layer_starts_from_hidden_state(mods, dev, T, use_xf):
+    # router projection inside the call (gate_w given, no logits) against the same layer fed with logits computed in float64
+    E, D, I, topk = 48, 512, 256, 4
+    ex, sh, _ = _layer(mods, dev, E, D, I, topk, 91)
+    g = torch.Generator().manual_seed(92)
+    gate_w = (torch.randn(E, D, generator=g) / D ** 0.5 * 3).float()
+    layer = mods.moe.MoELayer(ex["w13"].to(dev), ex["s13"].to(dev), ex["w2"].to(dev), ex["s2"].to(dev), n_experts=E, topk=topk,
+                              sh_w13=mods.w8.W8(sh["w13"].to(dev), sh["s13"].to(dev)), sh_w2=mods.w8.W8(sh["w2"].to(dev), sh["s2"].to(dev)),
+                              gate_w=gate_w.to(dev))
+    x = mods.synth.make_tokens(T, D, 93)
+    xf = (x.float() + 1e-3 * torch.randn(T, D, generator=g)) if use_xf else None
+    src = xf if use_xf else x.float()
+    logits = (src.double() @ gate_w.double().T).float()
+    want, eid_w, wt_w = layer.forward(x.to(dev), logits.to(dev), want_route=True)
+    got, eid_g, wt_g = layer.forward(x.to(dev), None, xf=xf.to(dev) if use_xf else None, want_route=True)
+    assert torch.equal(eid_g, eid_w)
+    assert torch.allclose(wt_g, wt_w, rtol=1e-4, atol=1e-7)
+    assert rel_err(got, want) < 1e-3
+    again = layer.forward(x.to(dev), None, xf=xf.to(dev) if use_xf else None)
+    assert torch.equal(again, got)  # the k-split sums are added in a fixed order: same logits, same routing, same output
+    assert mods.cukern.device_error(dev) == 0
