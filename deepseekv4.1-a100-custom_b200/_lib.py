@@ -54,6 +54,8 @@ _SIGNATURES = {
     "b200_mx_grouped_workspace_bytes": (c_sz, [c_i]),
     "b200_mx_grouped_gemm": (c_i, [c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_i, c_i, c_p, c_ll, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_f,
                                    c_i, c_p, c_ll, c_p, c_i, c_i, c_p, c_sz, c_p]),
+    "b200_hc_pre_norm_quant2": (c_i, [c_p, c_p, c_p, c_i, c_f, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
+    "b200_hc_post2": (c_i, [c_p, c_p, c_p, c_ll, c_ll, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_p]),
     "b200_device_error": (c_i, [c_p, c_p]),
 }
 

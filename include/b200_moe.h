@@ -206,6 +206,20 @@ int b200_mx_grouped_gemm(const void* w, long long w_estride, const void* s, long
                          int round_gu_bf16, void* out, long long out_ld, void* out_sf, int tokens_per_work, int rows_per_tile, void* workspace,
                          size_t workspace_bytes, cudaStream_t stream);
 
+/* ---- the steps either side of the MoE path in the reference's decode loop (hyper-connection mixes).
+ * b200_hc_pre_norm_quant2 replaces hc_pre_norm_quant2 (dsv41/fused2.py:171-246): x bf16 [rows, hc, dim], pre fp32 [rows, hc], norm weight
+ *   w [dim] (bf16, or fp32 with w_is_f32);  t = bf16(sum_h pre[h] * x[h]);  y = bf16(t / sqrt(mean(t^2) + eps) * w) bf16 [rows, dim];
+ *   yq = per-32 FP8 fake quantisation of y;  yf = y as fp32 (or NULL);  yqp = yq in the 8-k permuted order (or NULL).
+ *   dim % 32 == 0, hc <= 8, 16-byte aligned buffers.
+ * b200_hc_post2 replaces hc_post2_ (dsv41/fused2.py:505-558): residual bf16 [rows, hc, dim] is updated in place,
+ *   residual[i] <- bf16(post[i] * v + sum_h comb[h][i] * residual[h]),  post fp32 [rows, hc], comb fp32 [rows, hc, hc];
+ *   v = x bf16 [rows, dim] (nsum = 0) or bf16(sum_k y2[k] + ys): y2 fp32, element (row, k, c) at y2[row * y2_row_stride +
+ *   k * y2_sum_stride + c], ys bf16 [rows, dim] or NULL.  dim % 8 == 0. */
+int b200_hc_pre_norm_quant2(const void* x, const float* pre, const void* w, int w_is_f32, float eps, int rows, int hc, int dim, void* y, void* yq,
+                            float* yf, void* yqp, cudaStream_t stream);
+int b200_hc_post2(const void* x, const float* y2, const void* ys, long long y2_row_stride, long long y2_sum_stride, int nsum, void* residual,
+                  const float* post, const float* comb, int rows, int hc, int dim, cudaStream_t stream);
+
 /* ---- device error word.  Every device-side wait of this library is bounded; one that runs out of time stores a non-zero
  * code instead of hanging.  Synchronises `stream`, returns the code in *code (0 = none) and clears it. */
 int b200_device_error(int* code, cudaStream_t stream);

@@ -142,6 +142,46 @@ def moe_layer(x, logits, bias, w13, s13, w2, s2, shared, *, topk=6, temp=1.0, ro
     return {"out": out, "eid": eid, "wt": wt, "routed": routed}
 
 
+def hc_pre_norm_quant2(x: torch.Tensor, pre: torch.Tensor, w: torch.Tensor, eps: float):
+    """CPU restatement of the two passes of dsv41/fused2.py:171-211.  x bf16 [B, hc, d], pre fp32 [B, hc], w [d] -> (y bf16, yq bf16,
+    yqp bf16): pass 1 t = bf16(sum_h pre[h] * x[h]) accumulated in h order in fp32, var = sum(t^2) / d; pass 2
+    y = bf16(t * (1 / sqrt(var + eps)) * w), yq = per-32 FP8 fake quantisation, yqp = yq with every 8 k stored as 0,4,2,6,1,5,3,7."""
+    B, hc, d = x.shape
+    acc = torch.zeros(B, d, dtype=torch.float32)
+    for h in range(hc):
+        acc = acc + pre[:, h:h + 1].float() * x[:, h].float()
+    t = acc.to(torch.bfloat16).float()
+    var = (t.double() ** 2).sum(dim=1, keepdim=True).float() / d
+    y = (t * (1.0 / torch.sqrt(var + eps)) * w.float()).to(torch.bfloat16)
+    yq = fake_quant_fp8(y, 32)
+    perm = torch.tensor([0, 4, 2, 6, 1, 5, 3, 7])
+    yqp = yq.view(B, d // 8, 8)[:, :, perm].reshape(B, d)
+    return y, yq, yqp
+
+
+def hc_post2(residual: torch.Tensor, post: torch.Tensor, comb: torch.Tensor, x=None, y2=None, ys=None) -> torch.Tensor:
+    """CPU restatement of dsv41/fused2.py:505-536.  residual bf16 [B, hc, d], post fp32 [B, hc], comb fp32 [B, hc, hc]; v = x bf16 [B, d]
+    or bf16(sum_k y2[:, k] + ys) with y2 fp32 [B, nsum, d]; returns the new residual: out[i] = bf16(post[i] * v + sum_h comb[h][i] * r[h])."""
+    B, hc, d = residual.shape
+    if y2 is not None:
+        v = torch.zeros(B, d, dtype=torch.float32)
+        for k in range(y2.shape[1]):
+            v = v + y2[:, k].float()
+        if ys is not None:
+            v = v + ys.float()
+        v = v.to(torch.bfloat16).float()
+    else:
+        v = x.float()
+    r = residual.float()
+    out = torch.empty_like(residual)
+    for i in range(hc):
+        acc = post[:, i:i + 1].float() * v
+        for h in range(hc):
+            acc = acc + comb[:, h, i].float().unsqueeze(1) * r[:, h]
+        out[:, i] = acc.to(torch.bfloat16)
+    return out
+
+
 def group_pairs(expert: torch.Tensor, n_experts: int):
     expert = expert.to(torch.int32).contiguous()
     order = torch.empty(int((expert >= 0).sum()), dtype=torch.int32)

@@ -140,3 +140,30 @@ def test_moe_layer_composition(oracle):
         acc += oracle.moe_layer(x, logits, None, w13[start:start + n], s13[start:start + n], w2[start:start + n], s2[start:start + n], None, topk=topk,
                                 shard=(start, n), n_experts=E)["routed"]
     assert torch.allclose(acc, r["routed"], rtol=1e-6, atol=1e-6 * r["routed"].abs().max().item())
+
+
+def test_hc_restatements_basic_properties():
+    # dsv41/fused2.py:171-246, 505-558 restated on the CPU: identities that hold whatever the inputs
+    import torch
+    from oracle import oracle as O
+    g = torch.Generator().manual_seed(3)
+    B, hc, d = 2, 4, 128
+    x = torch.randn(B, hc, d, generator=g).to(torch.bfloat16)
+    w = torch.ones(d, dtype=torch.bfloat16)
+    pre = torch.zeros(B, hc)
+    pre[:, 2] = 1.0  # the pre-mix picks copy 2: y = rmsnorm(x[:, 2])
+    y, yq, yqp = O.hc_pre_norm_quant2(x, pre, w, 0.0)
+    t = x[:, 2].float()
+    want = (t / t.pow(2).mean(dim=1, keepdim=True).sqrt()).to(torch.bfloat16)
+    assert (y.float() - want.float()).abs().max() <= 2 ** -7 * want.float().abs().max()
+    assert torch.equal(yq.view(torch.int16), O.fake_quant_fp8(y, 32).view(torch.int16))
+    perm = [0, 4, 2, 6, 1, 5, 3, 7]
+    assert all(torch.equal(yqp[:, j], yq[:, perm[j]]) for j in range(8))
+    # post mix with post = 0 and comb = identity leaves the residual alone; with comb = 0 it broadcasts post * v
+    eye = torch.eye(hc).repeat(B, 1, 1)
+    assert torch.equal(O.hc_post2(x, torch.zeros(B, hc), eye, x=y), x)
+    out = O.hc_post2(x, torch.ones(B, hc), torch.zeros(B, hc, hc), x=y)
+    assert all(torch.equal(out[:, i], y) for i in range(hc))
+    y2 = torch.randn(B, 3, d, generator=g)
+    v = (y2.sum(dim=1) + y.float()).to(torch.bfloat16)
+    assert (O.hc_post2(x, torch.ones(B, hc), torch.zeros(B, hc, hc), y2=y2, ys=y)[:, 0].float() - v.float()).abs().max() <= 2 ** -7 * v.float().abs().max()
