@@ -1,6 +1,6 @@
 """Benchmark of the MoE-layer hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode64|decode32|decode8|decode1] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode64|decode32|decode8|decode1|prefill4096|fp8_gemv] [--impl reference]
     torchrun --nnodes=1 --nproc-per-node N ... bench.py --gpus N --steps K --warmup W      (N > 1: expert parallel)
 
 A step = one pass of the whole MoE layer (router -> input FP8 fake quantisation -> routed FP4 experts -> FP8 shared
@@ -11,6 +11,9 @@ Prints ONE JSON line (rank 0).  `value` = tokens/s with inputs resident in HBM; 
 with pinned HOST buffers (host->device and device->host copies inside the timed region); `roofline` = the dominant kernel
 (the routed gate/up weight stream) timed live with CUDA events against the measured HBM peak; `cpu_baseline` = the
 reference's own CPU expert chain timed on this box's host cores (N = 1 only).
+`roofline.prefill4096` (tensor bound), `roofline.decode` (the other decode batch sizes) and `roofline.fp8_gemv` (the dense FP8
+GEMV shapes M in {1,2,4,8} x N in {4096,12288,18432}, K = 4096) carry the other configurations of the same path; `parity` compares
+rows of one step with the CPU checker outside every timed region.
 `--impl reference` times only that CPU implementation, on the same workload and metric.
 """
 from __future__ import annotations
@@ -30,7 +33,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 E, D, I, TOPK = 384, 4096, 2048, 6
-WORKLOADS = {"decode64": 64, "decode32": 32, "decode8": 8, "decode1": 1, "prefill4096": 4096}
+WORKLOADS = {"decode64": 64, "decode32": 32, "decode8": 8, "decode1": 1, "prefill4096": 4096}   # + "fp8_gemv" (run_gpu)
 POOL = 12             # distinct (tokens, logits) sets cycled over the steps
 ROTATE = 29           # expert-id shift of the Zipf ranking between consecutive sets: hot experts change every step
 SEED = 1234
@@ -46,6 +49,14 @@ def measured_peaks():
         except Exception:
             pass
     return 6650.0, "fallback (6.65 TB/s)"
+
+
+def measured_tensor_sustained() -> float:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["bf16_tflops_sustained"])
+    except Exception:
+        return 1400.0
 
 
 def measured_tensor_peak():
@@ -214,7 +225,7 @@ def run_reference(args):
     rank, _, world = dist_env()
     if rank != 0:
         return
-    S = WORKLOADS[args.workload]
+    S = WORKLOADS.get(args.workload, 64)
     tps, dt, done, desc = time_cpu_chain(S, args.steps, args.warmup, budget_s=120.0)
     steps_done = max(1, done // S)
     line = {"impl": "reference", "metric": METRIC, "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -226,7 +237,7 @@ def run_reference(args):
 
 
 def workload_config(name: str, gpus: int) -> dict:
-    S = WORKLOADS[name]
+    S = WORKLOADS.get(name, 64)
     kind = "decode" if S <= 64 else "prefill"
     return {"workload": f"moe_{name}: {S} {kind} tokens, 384 experts (FP4 e2m1 + E8M0/32), hidden 4096, inter 2048, top-6 Zipf(s=1) softmax routing, "
                         f"+1 FP8 (e4m3 + E8M0 32x32) shared expert", "tokens": S, "experts": E, "hidden": D, "inter": I, "topk": TOPK,
@@ -265,6 +276,68 @@ def time_steps(fn, steps: int, warmup: int, barrier, finish=None):
     return e0.elapsed_time(e1) / steps  # ms per step
 
 
+def kernel_pass(layer, xs, ls, out, n: int, warmup: int):
+    """Separate short pass that times the dominant kernel alone: the library records a CUDA event pair around the routed gate/up
+    launch of every step (events on the launching stream).  Kept out of the pass that measures `value`, where the two event records
+    per step would sit between the chained launches.  Returns the mean launch duration in ms and the input set of every step."""
+    prof = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n + warmup)]
+    for a, b in prof:
+        a.record()
+        b.record()
+    torch.cuda.synchronize()
+    NP = len(xs)
+    for i in range(n + warmup):
+        layer.forward(xs[i % NP], ls[i % NP], out=out, prof_events=prof[i])
+    torch.cuda.synchronize()
+    durs = [prof[warmup + i][0].elapsed_time(prof[warmup + i][1]) for i in range(n)]
+    return statistics.mean(durs), [(warmup + i) % NP for i in range(n)]
+
+
+def parity_rows(layer_forward, synth, x_h, l_h, rows, fetch, shared, dev_rows_of):
+    """Compare `rows` of one batch with the CPU checker (outside every timed region): expert indices of the rows must be identical,
+    the bf16 output within 1e-2 of max |ref|.  layer_forward(x, logits) -> (out, eid) for the rows this rank holds; dev_rows_of maps
+    batch rows to the rank's local rows."""
+    from oracle import oracle as O
+    out, eid = layer_forward()
+    ref_eid, ref_wt = O.gate_topk(l_h[rows].float(), None, 1.0, TOPK, 1.0, "softmax", True)
+    ref = O.moe_rows(x_h[rows], ref_eid, ref_wt, fetch, shared, 10.0)
+    got = out[dev_rows_of].float().cpu()
+    want = ref["out"].float()
+    err = float((got - want).abs().max() / want.abs().max())
+    eq = bool(torch.equal(eid[dev_rows_of].cpu(), ref_eid)) if eid is not None else None
+    return {"max_rel_err": err, "eid_equal": eq, "tokens_checked": int(len(rows)), "tolerance": 1e-2, "ok": bool(err <= 1e-2 and eq is not False),
+            "checker": "oracle/ CPU restatement (pinned against the reference's own CPU library and goldens), rows of one step, outside the timed regions"}
+
+
+def bench_fp8_gemv(g, dev, steps: int, warmup: int, peak: float):
+    """Dense block-scaled FP8 GEMV (x bf16 [M, 4096] against e4m3 [N, 4096] with one fp32 scale per 128 x 128 block, bf16 out):
+    weights drawn as N(0, 0.02), quantised per block with scale = blockmax / 448.  Each shape cycles over enough weight copies to
+    exceed L2 (method of dsv41/bench_gemv_m1.py:50-68), timed with CUDA events around `steps` launches.  Algorithmic bytes = N*K
+    weight bytes + the scale bytes."""
+    synth, cukern = g._import("synth"), g._import("cukern")
+    K = 4096
+    res = {}
+    for N in (4096, 12288, 18432):
+        gen = torch.Generator(device=dev).manual_seed(SEED + N)
+        copies = max(3, -(-300_000_000 // (N * K)))
+        wf = torch.randn(N, K, generator=gen, device=dev) * 0.02
+        codes, scale = synth.quantize_fp8_block(wf, "f32b")
+        ws = [codes] + [codes.roll(i + 1, 0).contiguous() for i in range(copies - 1)]
+        del wf
+        for M in (1, 2, 4, 8):
+            x = torch.randn(M, K, generator=gen, device=dev).to(torch.bfloat16)
+            out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+            ms = time_steps(lambda i: cukern.fp8_gemm_tc(x, ws[i % copies], scale, out_dtype=torch.bfloat16, permuted=False, out=out), steps, warmup, lambda: None)
+            alg = N * K + scale.numel() * 4
+            gbs = alg / (ms * 1e-3) / 1e9
+            res[f"M{M}_N{N}"] = {"us": ms * 1e3, "gbs": gbs, "frac": gbs / peak, "algorithmic_bytes": alg, "weight_copies_cycled": copies}
+        del ws, codes
+        torch.cuda.empty_cache()
+    fr = [v["frac"] for v in res.values()]
+    return {"bound": "hbm", "unit": "GB/s", "peak": peak, "format": "e4m3 + fp32 scale per 128x128 block", "kernel": "skinny_kernel<FP8_F32B, STORE_BF16>",
+            "frac_min": min(fr), "frac_max": max(fr), "frac_mean": statistics.mean(fr), "shapes": res}
+
+
 def run_gpu(args):
     import __graft_entry__ as g
     rank, local_rank, world = dist_env()
@@ -272,7 +345,7 @@ def run_gpu(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     g.load_package()
-    synth, moe, w8, ep = g._import("synth"), g._import("moe"), g._import("w8"), g._import("ep")
+    synth, moe, w8, ep, cukern = g._import("synth"), g._import("moe"), g._import("w8"), g._import("ep"), g._import("cukern")
     import torch.distributed as dist
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -288,44 +361,74 @@ def run_gpu(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    peak, peak_src = measured_peaks()
+    tpeak, tsrc = measured_tensor_peak()
+    if args.workload == "fp8_gemv":
+        assert world == 1, "the FP8 GEMV workload is a single-GPU measurement"
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        r = bench_fp8_gemv(g, dev, args.steps, args.warmup, peak)
+        best = max(r["shapes"].values(), key=lambda v: v["gbs"])
+        line = {"metric": "FP8 dense GEMV GB/s (config 1: M in {1,2,4,8}, N in {4096,12288,18432}, K=4096)", "value": r["frac_mean"] * peak, "unit": "GB/s",
+                "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": statistics.mean(v["us"] for v in r["shapes"].values()) / 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": "fp8_gemv: x bf16 [M,4096] @ e4m3 [N,4096] (fp32 scale per 128x128), mean over 12 shapes", "l2": "weight copies cycled past L2"},
+                "clocks": sampler.stop(), "roofline": dict(r, achieved=best["gbs"], frac=best["frac"], traffic=None, peak_source=peak_src), "gpu_launches": 12 * args.steps}
+        print(json.dumps(line), flush=True)
+        return
+
     S = WORKLOADS[args.workload]
     start, n_local = ep.shard_ranges(E, world)[rank]
     # identical expert bits on every rank: the full layer is generated on the device from one seed, the rank keeps its slice
     ex = synth.make_experts(E, D, I, seed=SEED, device=dev)
-    if world > 1:
-        ex = {k: v[start:start + n_local].clone() for k, v in ex.items()}
-        torch.cuda.empty_cache()
-    sh = synth.make_shared(D, I, seed=SEED + 1, kind="e8m0", device=dev)
-    layer = moe.MoELayer(ex["w13"], ex["s13"], ex["w2"], ex["s2"], n_experts=E, topk=TOPK, sh_w13=w8.W8(sh["w13"], sh["s13"]), sh_w2=w8.W8(sh["w2"], sh["s2"]),
-                         swiglu_limit=10.0, shard_start=start, engine=args.engine)
+    sh_h = synth.make_shared(D, I, seed=SEED + 1, kind="e8m0")
     xs_h, ls_h = build_inputs(synth, S, dev)
     counts = [c for _, c in ep.split_tokens(S, world)]
     first = sum(counts[:rank])
     T_r = counts[rank]
+    # experts the parity rows (rank 0's first rows of input set 0) route to, fetched to the host before the layer is sliced
+    n_check = min(8, T_r)
+    par_fetch = None
+    if rank == 0 and not args.no_parity:
+        from oracle import oracle as O
+        pe, _ = O.gate_topk(ls_h[0][:n_check].float(), None, 1.0, TOPK, 1.0, "softmax", True)
+        ids = sorted(set(pe.reshape(-1).tolist()))
+        host = {k: ex[k][torch.tensor(ids, device=dev)].cpu() for k in ("w13", "s13", "w2", "s2")}
+        pos = {e: i for i, e in enumerate(ids)}
+        par_fetch = lambda want: tuple(host[k][[pos[e] for e in want]] for k in ("w13", "s13", "w2", "s2"))
+    if world > 1:
+        ex = {k: v[start:start + n_local].clone() for k, v in ex.items()}
+        torch.cuda.empty_cache()
+    sh = {k: v.to(dev) for k, v in sh_h.items()}
+    layer = moe.MoELayer(ex["w13"], ex["s13"], ex["w2"], ex["s2"], n_experts=E, topk=TOPK, sh_w13=w8.W8(sh["w13"], sh["s13"]), sh_w2=w8.W8(sh["w2"], sh["s2"]),
+                         swiglu_limit=10.0, shard_start=start, engine=args.engine)
     xs = [x[first:first + T_r].to(dev) for x in xs_h]
     ls = [l[first:first + T_r].to(dev) for l in ls_h]
     out = torch.empty(T_r, D, device=dev, dtype=torch.bfloat16)
     epl = ep.EPMoE(layer) if world > 1 else None
 
-    # unique experts touched per input set (bookkeeping for the byte counts; untimed)
-    NP = pool_size(S)
-    uniq = []
-    for i in range(NP):
-        _, eid, _ = layer.forward(xs_h[i].to(dev), ls_h[i].to(dev), want_route=True)
-        uniq.append(int(torch.unique(eid).numel()))
-    torch.cuda.synchronize()
+    # ---- parity of one step against the CPU checker (untimed)
+    parity = None
+    if world > 1 or not args.no_parity:
+        def fwd():
+            if world == 1:
+                o, e_, _ = layer.forward(xs[0], ls[0], want_route=True)
+                return o, e_
+            return epl.forward(xs[0], ls[0], counts), None
+        if rank == 0 and par_fetch is not None:
+            parity = parity_rows(fwd, synth, xs_h[0], ls_h[0], torch.arange(n_check), par_fetch, tuple(sh_h[k] for k in ("w13", "s13", "w2", "s2")), torch.arange(n_check, device=dev))
+        elif world > 1:
+            fwd()  # the other ranks take part in the exchange of that step
+        torch.cuda.synchronize()
 
-    # ---- value: inputs resident in HBM
-    prof = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps + args.warmup)]
-    for a, b in prof:
-        a.record()
-        b.record()
-    torch.cuda.synchronize()
+    # unique experts touched per input set (bookkeeping for the byte counts; untimed): from the logits, on the host
+    NP = pool_size(S)
+    uniq = [int(torch.unique(l.float().topk(TOPK, dim=-1).indices).numel()) for l in ls_h]
 
     def step_resident(i):
         j = i % NP
         if world == 1:
-            layer.forward(xs[j], ls[j], out=out, prof_events=prof[i])
+            layer.forward(xs[j], ls[j], out=out)
         else:
             out.copy_(epl.forward(xs[j], ls[j], counts))
 
@@ -385,83 +488,121 @@ def run_gpu(args):
     h2d = (nbx + nbl) * world
     d2h = T_r * D * 2 * world
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-
-    peak, peak_src = measured_peaks()
-    exp_b13 = 2 * I * D // 2 + 2 * I * D // 32
+    exp_b = synth.expert_bytes(D, I)
+    sh_b = synth.shared_bytes(D, I, "e8m0")
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.workload, world), "clocks": clocks,
             "e2e": {"value": S / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
-            "gpu_launches": ((8 if S > 64 else (5 if layer._use_mx(T_r * world) else 6)) + (0 if world == 1 else 1)) * args.steps}
-    if world == 1:
-        durs = [prof[args.warmup + i][0].elapsed_time(prof[args.warmup + i][1]) for i in range(args.steps)]
-        u_steps = [uniq[(args.warmup + i) % NP] for i in range(args.steps)]
-        avg_ms = statistics.mean(durs)
-        layer_bytes = statistics.mean(u_steps) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
-        if S <= 64:
-            mx = layer._use_mx(S)
-            # the tensor-core launch streams the shared expert's gate/up matrix (FP8 + 32x32 scales) in the same kernel
-            alg = statistics.mean(u_steps) * exp_b13 + ((2 * I * D + 2 * I * D // 1024) if mx else 0)
-            achieved = alg / (avg_ms * 1e-3) / 1e9
-            # DRAM bytes per launch: (dram__bytes_read + dram__bytes_write) / algorithmic bytes of the same kernel in the committed ncu
-            # captures (profiles/mx_gemm_kernel_decode64_e96_ncu_full.md: 0.990; profiles/skinny_fp4_decode8_ncu_full.md: 1.075),
-            # scaled to this launch by its algorithmic bytes (traffic grows with the experts streamed)
-            traffic = alg * (0.990 if mx else 1.075)
-            line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-                                "traffic_source": "ncu capture of a smaller case, scaled by algorithmic bytes",
-                                "kernel": ("mx_gemm_kernel (gate/up weight stream of the routed experts and the shared expert on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)" if mx
-                                           else "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"),
-                                "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src,
-                                "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": statistics.mean(u_steps),
-                                "whole_layer": {"bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
-                                                "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak}}
-        else:
-            tpeak, tsrc = measured_tensor_peak()
-            flops1 = S * (TOPK + 1) * 2.0 * D * 2 * I    # gate/up GEMM of the routed experts and the shared expert (the timed kernel)
-            flops_layer = S * (TOPK + 1) * (2.0 * D * 2 * I + 2.0 * I * D)
-            achieved = flops1 / (avg_ms * 1e-3) / 1e12
-            line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": tpeak, "unit": "TFLOP/s", "frac": achieved / tpeak, "traffic": None,
-                                "kernel": "mx_gemm_kernel (gate/up grouped GEMM of routed + shared experts, tcgen05 kind::mxf8f6f4 block-scaled, + SwiGLU + FP8 quant)",
-                                "algorithmic_flops_per_launch": flops1, "avg_launch_ms": avg_ms, "peak_source": tsrc,
-                                "unique_experts_per_step": statistics.mean(u_steps),
-                                "whole_layer": {"flops_per_step": flops_layer, "achieved_tflops": flops_layer / (ms * 1e-3) / 1e12,
-                                                "frac": flops_layer / (ms * 1e-3) / 1e12 / tpeak, "weight_bytes_per_step": layer_bytes,
-                                                "weight_stream_floor_ms": layer_bytes / (peak * 1e9) * 1e3}}
-        # other decode batch sizes of the same configuration (short runs, same method)
-        sweep = {}
-        if not args.no_sweep:
-            for name, s2 in WORKLOADS.items():
-                if name == args.workload:
-                    continue
-                xs2, ls2 = build_inputs(synth, s2, dev)
-                xs2, ls2 = [x.to(dev) for x in xs2], [l.to(dev) for l in ls2]
-                o2 = torch.empty(s2, D, device=dev, dtype=torch.bfloat16)
-                np2 = pool_size(s2)
-                u2 = []
-                for i in range(np2):
-                    _, eid, _ = layer.forward(xs2[i], ls2[i], want_route=True)
-                    u2.append(int(torch.unique(eid).numel()))
-                k2 = args.steps if s2 <= 64 else max(3, min(args.steps, 8))
-                m2 = time_steps(lambda i: layer.forward(xs2[i % np2], ls2[i % np2], out=o2), k2, args.warmup, barrier)
-                b2 = statistics.mean(u2) * synth.expert_bytes(D, I) + synth.shared_bytes(D, I, "e8m0")
-                sweep[name] = {"tokens_per_s": s2 / (m2 * 1e-3), "ms_per_step": m2, "unique_experts": statistics.mean(u2), "layer_gbs": b2 / (m2 * 1e-3) / 1e9,
-                               "layer_hbm_frac": b2 / (m2 * 1e-3) / 1e9 / peak}
-                if s2 > 64:
-                    f2 = s2 * (TOPK + 1) * (2.0 * D * 2 * I + 2.0 * I * D)
-                    sweep[name]["tflops"] = f2 / (m2 * 1e-3) / 1e12
-                    sweep[name]["frac_of_bf16_peak"] = f2 / (m2 * 1e-3) / 1e12 / measured_tensor_peak()[0]
-                del xs2, ls2, o2
-        line["sweep"] = sweep
-        if not args.no_cpu:
-            tps, dt, done, desc = time_cpu_chain(S, 10 ** 9, 1, budget_s=args.cpu_seconds)
-            line["cpu_baseline"] = dict(value=tps, unit="tokens/s", **desc)
-    print(json.dumps(line), flush=True)
+            "gpu_launches": layer.launches_per_step(T_r * world) * args.steps}
+    if parity is not None:
+        line["parity"] = parity
+
     if world > 1:
+        # ---- expert-parallel line: bytes of the rank that streams most, the exchange's share, and the prefill half of the configuration
+        mine = [int(((torch.unique(l.float().topk(TOPK, dim=-1).indices) >= start) & (torch.unique(l.float().topk(TOPK, dim=-1).indices) < start + n_local)).sum())
+                for l in ls_h]
+        t = torch.tensor([statistics.mean(mine)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        max_rank_bytes = float(t.item()) * exp_b + epl.shared_bytes_per_rank(sh_b)
+        phases = epl.time_phases(xs[0], ls[0], counts, reps=20) if hasattr(epl, "time_phases") else None
+        if phases is not None:
+            for k in list(phases):
+                phases[k] = max_over_ranks(phases[k])
+        pre = None
+        if not args.no_sweep:
+            Tp = 16384
+            cp = [c for _, c in ep.split_tokens(Tp, world)]
+            fp = sum(cp[:rank])
+            xp = [synth.make_tokens(Tp, D, SEED + 40 + i)[fp:fp + cp[rank]].to(dev) for i in range(2)]
+            lp = [synth.make_logits(Tp, E, SEED + 3, topk=TOPK, rotate=ROTATE * i)[fp:fp + cp[rank]].to(dev) for i in range(2)]
+            msp = max_over_ranks(time_steps(lambda i: epl.forward(xp[i & 1], lp[i & 1], cp), 5, 3, barrier))
+            fl = Tp * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)
+            pre = {"tokens": Tp, "ms_per_step": msp, "tokens_per_s": Tp / (msp * 1e-3), "routed_tflops_all_gpus": fl / (msp * 1e-3) / 1e12,
+                   "frac_of_bf16_burst_per_gpu": fl / (msp * 1e-3) / 1e12 / world / tpeak}
+            del xp, lp
+        if rank == 0:
+            gbs = max_rank_bytes / (ms * 1e-3) / 1e9
+            line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_source": peak_src,
+                                "what": "whole step of the rank that streams most: (its distinct local experts x 13,369,344 B + its share of the shared expert) / max-over-ranks step time",
+                                "max_rank_bytes_per_step": max_rank_bytes, "phases_ms": phases}
+            if pre is not None:
+                line["prefill16384"] = pre
+            code = cukern.device_error(dev)
+            line["device_error"] = code
+            print(json.dumps(line), flush=True)
         dist.destroy_process_group()
+        return
+
+    # ---- single GPU: kernel-level roofline from a separate short pass with events around the dominant kernel
+    n_k = min(args.steps, 60)
+    avg_ms, sets = kernel_pass(layer, xs, ls, out, n_k, args.warmup)
+    u_k = statistics.mean(uniq[j] for j in sets)
+    u_all = statistics.mean(uniq[(args.warmup + i) % NP] for i in range(args.steps))
+    layer_bytes = u_all * exp_b + sh_b
+    exp_b13 = 2 * I * D // 2 + 2 * I * D // 32
+
+    def prefill_roofline(ms_step: float, k_ms: float | None, u: float):
+        fl_routed = S_PRE * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)          # routed pairs only: pairs x 50,331,648
+        fl_all = S_PRE * (TOPK + 1) * (2.0 * D * 2 * I + 2.0 * I * D)      # + the shared expert's rows
+        ach = fl_routed / (ms_step * 1e-3) / 1e12
+        r = {"bound": "tensor", "achieved": ach, "peak": tpeak, "unit": "TFLOP/s", "frac": ach / tpeak, "traffic": None, "peak_source": tsrc,
+             "what": "whole layer step (route, bucketing, quantisation, both grouped GEMMs, combine); FLOPs = routed pairs x 50,331,648",
+             "frac_of_sustained": ach / measured_tensor_sustained(), "ms_per_step": ms_step, "tokens_per_s": S_PRE / (ms_step * 1e-3),
+             "with_shared_expert": {"achieved": fl_all / (ms_step * 1e-3) / 1e12, "frac": fl_all / (ms_step * 1e-3) / 1e12 / tpeak},
+             "weight_stream_floor_ms": (u * exp_b + sh_b) / (peak * 1e9) * 1e3, "unique_experts_per_step": u}
+        if k_ms is not None:
+            f1 = S_PRE * (TOPK + 1) * 2.0 * D * 2 * I
+            r["gate_up_kernel"] = {"kernel": "mx_gemm_kernel (gate/up grouped GEMM of routed + shared rows, tcgen05 kind::mxf8f6f4, + SwiGLU + FP8 quantisation)",
+                                   "avg_launch_ms": k_ms, "achieved": f1 / (k_ms * 1e-3) / 1e12, "frac": f1 / (k_ms * 1e-3) / 1e12 / tpeak}
+        return r
+
+    S_PRE = 4096
+    if S <= 64:
+        mx = layer._use_mx(S)
+        # the tensor-core launch streams the shared expert's gate/up matrix (FP8 + 32x32 scales) in the same kernel
+        alg = u_k * exp_b13 + ((2 * I * D + 2 * I * D // 1024) if mx else 0)
+        achieved = alg / (avg_ms * 1e-3) / 1e9
+        # DRAM bytes per launch: (dram__bytes_read + dram__bytes_write) / algorithmic bytes of the same kernel in the committed ncu
+        # capture of a smaller case, scaled to this launch by its algorithmic bytes (traffic grows with the experts streamed)
+        ratio = layer.traffic_ratio(S)
+        line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": alg * ratio,
+                            "traffic_source": "ncu capture of a smaller case (profiles/), scaled by algorithmic bytes",
+                            "kernel": layer.dominant_kernel(S),
+                            "algorithmic_bytes_per_launch": alg, "avg_launch_ms": avg_ms, "peak_source": peak_src, "timed_in": f"separate pass of {n_k} steps with an event pair around the kernel",
+                            "frac_of_8TBs_nominal": achieved / 8000.0, "unique_experts_per_step": u_k,
+                            "whole_layer": {"bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes / (ms * 1e-3) / 1e9,
+                                            "frac": layer_bytes / (ms * 1e-3) / 1e9 / peak}}
+    else:
+        line["roofline"] = prefill_roofline(ms, avg_ms, u_all)
+    # ---- the other batch sizes of the same configuration (short runs, same method), and the dense FP8 GEMV shapes
+    if not args.no_sweep:
+        dec = {}
+        for name, s2 in WORKLOADS.items():
+            if name == args.workload:
+                continue
+            xs2, ls2 = build_inputs(synth, s2, dev)
+            u2 = statistics.mean(int(torch.unique(l.float().topk(TOPK, dim=-1).indices).numel()) for l in ls2)
+            xs2, ls2 = [x.to(dev) for x in xs2], [l.to(dev) for l in ls2]
+            o2 = torch.empty(s2, D, device=dev, dtype=torch.bfloat16)
+            np2 = pool_size(s2)
+            k2 = args.steps if s2 <= 64 else max(3, min(args.steps, 8))
+            m2 = time_steps(lambda i: layer.forward(xs2[i % np2], ls2[i % np2], out=o2), k2, args.warmup, barrier)
+            if s2 > 64:
+                km, _ = kernel_pass(layer, xs2, ls2, o2, 3, 2)
+                line["roofline"]["prefill4096"] = prefill_roofline(m2, km, u2)
+            else:
+                b2 = u2 * exp_b + sh_b
+                dec[name] = {"bound": "hbm", "tokens_per_s": s2 / (m2 * 1e-3), "ms_per_step": m2, "unique_experts": u2, "achieved": b2 / (m2 * 1e-3) / 1e9, "unit": "GB/s",
+                             "frac": b2 / (m2 * 1e-3) / 1e9 / peak, "what": "whole layer step: (distinct experts x 13,369,344 B + shared expert) / step time"}
+            del xs2, ls2, o2
+        line["roofline"]["decode"] = dec
+        line["roofline"]["fp8_gemv"] = bench_fp8_gemv(g, dev, min(args.steps, 100), args.warmup, peak)
+    line["device_error"] = cukern.device_error(dev)
+    if not args.no_cpu:
+        tps, dt, done, desc = time_cpu_chain(S, 10 ** 9, 1, budget_s=args.cpu_seconds)
+        line["cpu_baseline"] = dict(value=tps, unit="tokens/s", **desc)
+    print(json.dumps(line), flush=True)
 
 
 def main():
@@ -470,8 +611,9 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS) + ["fp8_gemv"])
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--engine", type=int, default=0, choices=[0, 1, 2], help="0 automatic, 1 weight-streaming kernels, 2 tcgen05 block-scaled kernels")

@@ -323,7 +323,7 @@ extern "C" int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8,
     rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, work, n_work, n_pairs, stream);
     if (rc) return rc;
     if (zero_out && !accumulate) {
-        rc = skinny_zero_foreign(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, out, out_ld, N, stream);
+        rc = skinny_zero_foreign(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, pair_out, out, out_ld, N, stream);
         if (rc) return rc;
     }
     return skinny_launch(a, fmt, epi, stream);
@@ -594,7 +594,12 @@ extern "C" int b200_mx_quantize_rows(const void* x, long long x_ld, const int* s
 
 extern "C" int b200_device_error(int* code, cudaStream_t stream) {
     if (!code) return ERR_BAD_ARG;
-    return mx_device_error(code, stream);
+    int mx = 0, sk = 0;
+    int rc = mx_device_error(&mx, stream);  // synchronises the stream
+    if (rc) return rc;
+    if ((rc = skinny_device_error(&sk))) return rc;
+    *code = mx ? mx : (sk ? 1000 + sk : 0);  // tensor-core kernels report 11..41, the streaming kernels 1001..1091
+    return 0;
 }
 
 extern "C" size_t b200_mx_grouped_workspace_bytes(int n_rows) {

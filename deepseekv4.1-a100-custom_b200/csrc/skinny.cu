@@ -453,19 +453,27 @@ __global__ void __launch_bounds__(1024) skinny_plan_kernel(const int* __restrict
         if (tid == 0) running += tot;
         __syncthreads();
     }
-    if (tid == 0) *n_work = running < max_work ? running : max_work;
+    if (tid == 0) {
+        *n_work = running < max_work ? running : max_work;
+        if (running > max_work) atomicCAS(&g_skinny_error, 0, 91);  // the groups need more works than the list holds: results are incomplete
+    }
 }
 
+// Zeroes the output rows of the pairs of foreign groups.  Pair p writes row pair_out[p] (p itself without pair_out), so that is the
+// row cleared here too.
 __global__ void skinny_zero_foreign_kernel(const int* __restrict__ grp_expert, const int* __restrict__ grp_start, const int* __restrict__ grp_count,
-                                           int G, int n_pairs, int shard_start, int shard_n, float* __restrict__ out, long long out_ld, int N) {
+                                           int G, int n_pairs, int shard_start, int shard_n, const int* __restrict__ pair_out, float* __restrict__ out,
+                                           long long out_ld, int N) {
     for (int gi = blockIdx.x; gi < G; gi += gridDim.x) {
         const int e = grp_expert[gi] - shard_start;
         if (e >= 0 && e < shard_n) continue;
         int s = grp_start[gi], en = grp_count ? s + grp_count[gi] : grp_start[gi + 1];
         if (en > n_pairs) en = n_pairs;
         if (s < 0) s = 0;
-        for (int r = s; r < en; ++r)
-            for (int n = threadIdx.x; n < N; n += blockDim.x) out[(long long)r * out_ld + n] = 0.f;
+        for (int r = s; r < en; ++r) {
+            const long long row = pair_out ? pair_out[r] : r;
+            for (int n = threadIdx.x; n < N; n += blockDim.x) out[row * out_ld + n] = 0.f;
+        }
     }
 }
 
@@ -546,6 +554,19 @@ int skinny_launch(const SkinnyArgs& a_in, int fmt, int epi, cudaStream_t stream)
     return ERR_UNSUPPORTED;
 }
 
+// copies and clears the device error word of the streaming kernels (the caller has synchronised the stream)
+int skinny_device_error(int* out) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_skinny_error, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (v) {
+        int z = 0;
+        cudaMemcpyToSymbol(g_skinny_error, &z, sizeof(int));
+    }
+    *out = v;
+    return 0;
+}
+
 int skinny_plan(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n, int4* work,
                 int* n_work, int max_work, cudaStream_t stream, int tpw) {
     skinny_plan_kernel<<<1, 1024, 0, stream>>>(grp_expert, grp_start, grp_count, G, n_pairs, shard_start, shard_n, work, n_work, max_work, tpw);
@@ -554,9 +575,9 @@ int skinny_plan(const int* grp_expert, const int* grp_start, const int* grp_coun
 }
 
 int skinny_zero_foreign(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n,
-                        float* out, long long out_ld, int N, cudaStream_t stream) {
+                        const int* pair_out, float* out, long long out_ld, int N, cudaStream_t stream) {
     int grid = G < 1024 ? (G > 0 ? G : 1) : 1024;
-    skinny_zero_foreign_kernel<<<grid, 256, 0, stream>>>(grp_expert, grp_start, grp_count, G, n_pairs, shard_start, shard_n, out, out_ld, N);
+    skinny_zero_foreign_kernel<<<grid, 256, 0, stream>>>(grp_expert, grp_start, grp_count, G, n_pairs, shard_start, shard_n, pair_out, out, out_ld, N);
     B200_CHECK_LAUNCH();
     return 0;
 }

@@ -50,11 +50,12 @@ struct SkinnyArgs {
 };
 
 int sm_count();
+int skinny_device_error(int* out);  // device error word of the streaming kernels (1-3: a wait ran out of time, 91: work list overflow)
 int skinny_check(const SkinnyArgs& a, int fmt, int epi);
 int skinny_launch(const SkinnyArgs& a, int fmt, int epi, cudaStream_t stream);
 int skinny_plan(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n, int4* work,
                 int* n_work, int max_work, cudaStream_t stream, int tpw = SK_TOK);
 int skinny_zero_foreign(const int* grp_expert, const int* grp_start, const int* grp_count, int G, int n_pairs, int shard_start, int shard_n,
-                        float* out, long long out_ld, int N, cudaStream_t stream);
+                        const int* pair_out, float* out, long long out_ld, int N, cudaStream_t stream);
 
 }  // namespace b200

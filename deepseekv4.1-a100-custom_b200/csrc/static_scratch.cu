@@ -21,8 +21,8 @@
 namespace b200 {
 
 constexpr int STATIC_MAX_PAIRS = B200_STATIC_MAX_PAIRS;                       // 4096 pairs
-constexpr size_t STATIC_WORK_BYTES = ((size_t)STATIC_MAX_PAIRS + 1) * 16;     // int4 work list
-constexpr size_t STATIC_SCRATCH_BYTES = STATIC_WORK_BYTES + 256;              // + the work count, on its own 256-byte line: 65,808 bytes
+constexpr size_t STATIC_WORK_BYTES = (((size_t)STATIC_MAX_PAIRS + 1) * 16 + 255) & ~(size_t)255;  // int4 work list, rounded up to 256 bytes
+constexpr size_t STATIC_SCRATCH_BYTES = STATIC_WORK_BYTES + 256;              // + the work count on the 256-byte line behind it: 66,048 bytes
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_SCRATCH_BYTES];
 
@@ -82,7 +82,7 @@ extern "C" int b200_fp4_grouped_gemm_static(const void* x, long long x_ld, int x
     rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, work, n_work, n_pairs, stream);
     if (rc) return rc;
     if (zero_out && !accumulate) {
-        rc = skinny_zero_foreign(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, out, out_ld, N, stream);
+        rc = skinny_zero_foreign(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, pair_out, out, out_ld, N, stream);
         if (rc) return rc;
     }
     return skinny_launch(a, fmt, epi, stream);

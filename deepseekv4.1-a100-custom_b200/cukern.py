@@ -138,13 +138,14 @@ def fp8_gemv_m1(x: torch.Tensor, w8: torch.Tensor, s8: torch.Tensor, group_cols:
     return _fp8(x, w8, s8, True, torch.bfloat16, out)
 
 
-def fp8_gemm_tc(x: torch.Tensor, w8: torch.Tensor, s8: torch.Tensor, group_cols: int = 0, out_dtype=torch.bfloat16, permuted: bool = True) -> torch.Tensor:
+def fp8_gemm_tc(x: torch.Tensor, w8: torch.Tensor, s8: torch.Tensor, group_cols: int = 0, out_dtype=torch.bfloat16, permuted: bool = True,
+                out: torch.Tensor | None = None) -> torch.Tensor:
     """x bf16 [M, K]; w8 uint8 e4m3 [N, K] in the w8.PERM_K byte order (permuted=False: natural order); s8 uint8 E8M0
     [ceil(N/32), K/32] or fp32 [ceil(N/128), ceil(K/128)].  Returns x @ dequant(w8, s8)^T as [M, N]  (dsv41/cukern.py:165-221)."""
     if group_cols:
         raise NotImplementedError("block-diagonal use (attention o-projection) is outside the MoE path")
     assert x.is_contiguous()
-    return _fp8(x, w8, s8, permuted, out_dtype)
+    return _fp8(x, w8, s8, permuted, out_dtype, out)
 
 
 # --------------------------------------------------------------------------- expert-parallel helpers

@@ -53,6 +53,10 @@ class EPMoE:
         self.partial_fn = partial_fn or self._partial_cuda
         self.shared_fn = shared_fn or self._shared_cuda
 
+    def shared_bytes_per_rank(self, shared_bytes: int) -> float:
+        """Bytes of the shared expert one rank streams per step (every rank streams all of it)."""
+        return float(shared_bytes)
+
     # ---- CUDA defaults
     def _partial_cuda(self, x_all, logits_all):
         return self.layer.forward(x_all, logits_all, final=False, want_routed=True)

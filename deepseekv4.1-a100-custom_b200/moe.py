@@ -56,6 +56,23 @@ class MoELayer:
     def _use_mx(self, tokens: int) -> bool:
         return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 0)
 
+    # ---- facts about one forward() that a benchmark reports next to its timings
+    def launches_per_step(self, tokens: int) -> int:
+        """Kernels of this library one forward() launches for `tokens` tokens."""
+        if tokens * self.topk > 4096:
+            return 8   # route, histogram, scan, scatter, quantise, gate/up GEMM, down GEMM, finalise
+        return 5 if self._use_mx(tokens) else (6 if self.sh_w13 is not None else 4)
+
+    def dominant_kernel(self, tokens: int) -> str:
+        if self._use_mx(tokens):
+            return "mx_gemm_kernel (gate/up weight stream of the routed experts and the shared expert on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)"
+        return "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"
+
+    def traffic_ratio(self, tokens: int) -> float:
+        """DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the profiler captures of a smaller case
+        (profiles/mx_gemm_kernel_decode64_e96_ncu_full.md, profiles/skinny_fp4_decode8_ncu_full.md)."""
+        return 0.990 if self._use_mx(tokens) else 1.075
+
     def shared_expert(self, x: torch.Tensor) -> torch.Tensor | None:
         """The shared expert alone: x bf16 [T, D] -> ys bf16 [T, D] (None without one); the values of dsv41/model.py:1635-1638 on FP8
         fake-quantised activations.  Tensor-core kernels when the layer would use them for T tokens, else the streaming ones."""

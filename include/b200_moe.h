@@ -4,9 +4,11 @@
  *
  * Conventions (the ones dsv41/cukern.py:1-57 sets for the reference's launchers):
  *   - every pointer is a DEVICE pointer on the current CUDA device unless the comment says "host";
- *   - every call only enqueues work on `stream`; nothing synchronises, nothing allocates, so calls are
- *     capturable in a CUDA graph.  Scratch memory is passed in by the caller (`workspace`), sized by the
- *     matching *_workspace_bytes function;
+ *   - every call only enqueues work on `stream` and nothing allocates.  The one call that synchronises is
+ *     b200_device_error (it waits for `stream` and reads the device error word).  Scratch memory is passed in
+ *     by the caller (`workspace`), sized by the matching *_workspace_bytes function, except for
+ *     b200_fp4_grouped_gemm_static, whose scratch is a fixed array inside the library;
+ *   - b200_hc_post2 and b200_sum_rows put rows / groups on the grid's y dimension: at most 65,535 of them per call;
  *   - return value: 0 = ok; > 0 = the cudaError_t of a failed runtime call; < 0 = argument error
  *     (B200_ERR_* below) detected before anything was launched;
  *   - "bf16" = 16-bit bfloat, "e4m3" = float8_e4m3fn bit patterns, "E8M0" = one byte b meaning 2^(b-127),
@@ -102,7 +104,7 @@ int b200_fp4_grouped_gemm(const void* x, long long x_ld, int x_perm8, const void
 
 /* ---- the same grouped FP4 expert GEMM with its scratch inside the library: no workspace argument, and the call obtains no
  * memory from the CUDA runtime or anyone else.  No counterpart in the reference.  Arguments, kernels and results are those of
- * b200_fp4_grouped_gemm.  The work list lives in one fixed array per device (about 64 KB, part of the library's device
+ * b200_fp4_grouped_gemm.  The work list lives in one fixed array per device (66,048 bytes, part of the library's device
  * image), so n_pairs is limited to B200_STATIC_MAX_PAIRS; more returns B200_ERR_TOO_LARGE and launches nothing.
  *   - set-up: the first call on each device looks the array's address up (cudaGetSymbolAddress, result cached); make that
  *     call before any stream capture begins;

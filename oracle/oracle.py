@@ -142,6 +142,42 @@ def moe_layer(x, logits, bias, w13, s13, w2, s2, shared, *, topk=6, temp=1.0, ro
     return {"out": out, "eid": eid, "wt": wt, "routed": routed}
 
 
+def moe_rows(x_rows, eid, wt, fetch_experts, shared, limit: float = 10.0, shard=(0, 1 << 30)):
+    """The layer for a few token rows of a batch whose expert set is too large for the host (all 384 experts of the benchmark
+    layer are 5.1 GB): the same steps as `moe_layer`, composed from the pinned pieces (fake quantisation -> gate/up pairs ->
+    SwiGLU * weight + quantisation -> down pairs -> sum in slot order -> + shared expert -> bf16), on the experts the rows route to.
+    x_rows bf16 [n, D]; eid int32 [n, topk] / wt fp32 [n, topk]: the routing of those rows (checked separately against
+    `gate_topk`); fetch_experts(ids: list[int]) -> (w13, s13, w2, s2) CPU uint8 tensors stacked in the order of `ids`;
+    shared = None or (sh_w13, sh_s13, sh_w2, sh_s2); shard = (start, n): only experts of that range contribute to `routed`.
+    Returns dict(out bf16 [n, D], routed fp32 [n, D])."""
+    x_rows = _u16(x_rows)
+    n, D = x_rows.shape
+    topk = eid.shape[1]
+    xq = fake_quant_fp8(x_rows, 32)
+    e = eid.to(torch.int64).reshape(-1)
+    local = (e >= shard[0]) & (e < shard[0] + shard[1])
+    ids = sorted(set(e[local].tolist()))
+    routed = torch.zeros(n, D, dtype=torch.float32)
+    if ids:
+        w13, s13, w2, s2 = fetch_experts(ids)
+        inter = w2.shape[2] * 2
+        remap = {g: i for i, g in enumerate(ids)}
+        sel = local.nonzero().flatten()
+        P = sel.numel()
+        ex = torch.tensor([remap[int(g)] for g in e[sel]], dtype=torch.int32)
+        tok = (sel // topk).to(torch.int32)
+        rows = torch.arange(P, dtype=torch.int32)
+        gu = fp4_pairs(xq, w13, s13, ex, tok, rows, None, P)
+        h = swiglu_quant(gu, wt.reshape(-1)[sel], inter, limit)
+        y2 = fp4_pairs(h, w2, s2, ex, rows, rows, None, P)
+        for p in range(P):  # slot order within a token, as y2.view(T, topk, D).sum(1)
+            routed[int(tok[p])] += y2[p]
+    out = routed
+    if shared is not None:
+        out = routed + shared_expert(xq, *shared, limit).float()
+    return {"out": out.to(torch.bfloat16), "routed": routed}
+
+
 def hc_pre_norm_quant2(x: torch.Tensor, pre: torch.Tensor, w: torch.Tensor, eps: float):
     """CPU restatement of the two passes of dsv41/fused2.py:171-211.  x bf16 [B, hc, d], pre fp32 [B, hc], w [d] -> (y bf16, yq bf16,
     yqp bf16): pass 1 t = bf16(sum_h pre[h] * x[h]) accumulated in h order in fp32, var = sum(t^2) / d; pass 2

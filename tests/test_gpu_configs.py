@@ -1,0 +1,52 @@
+"""Parity at the sizes the benchmark runs: hidden 4096, expert width 2048, 384 resident experts, top-6 + FP8 shared expert, the
+benchmark's own Zipf(1.0) logits.  The expert tensors (5.1 GB) are generated on the device; the checker fetches only the experts
+the compared rows route to.  Gates: identical top-k expert indices for EVERY token, routing weights to 2e-5, max relative error
+(relative to max |ref|) <= 1e-2 on the bf16 output of the compared rows, <= 2e-3 on their fp32 routed sum."""
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+
+E, D, I, TOPK = 384, 4096, 2048, 6
+
+
+@pytest.fixture(scope="module")
+def full_layer(mods, dev):
+    ex = mods.synth.make_experts(E, D, I, seed=1234, device=dev)
+    sh = mods.synth.make_shared(D, I, seed=1235, kind="e8m0")
+    layer = mods.moe.MoELayer(ex["w13"], ex["s13"], ex["w2"], ex["s2"], n_experts=E, topk=TOPK, sh_w13=mods.w8.W8(sh["w13"].to(dev), sh["s13"].to(dev)),
+                              sh_w2=mods.w8.W8(sh["w2"].to(dev), sh["s2"].to(dev)), swiglu_limit=10.0)
+    fetch = lambda ids: tuple(ex[k][torch.tensor(ids, device=dev)].cpu() for k in ("w13", "s13", "w2", "s2"))
+    yield layer, fetch, (sh["w13"], sh["s13"], sh["w2"], sh["s2"])
+    del layer, ex
+    torch.cuda.empty_cache()
+
+
+def _compare(mods, oracle, dev, full_layer, T, rows, seed, rotate=0):
+    layer, fetch, shared = full_layer
+    x = mods.synth.make_tokens(T, D, seed)
+    logits = mods.synth.make_logits(T, E, seed + 1, topk=TOPK, rotate=rotate)
+    out, routed, eid, wt = layer.forward(x.to(dev), logits.to(dev), want_routed=True, want_route=True)
+    assert mods.cukern.device_error(dev) == 0
+    ref_eid, ref_wt = oracle.gate_topk(logits.float(), None, 1.0, TOPK, 1.0, "softmax", True)
+    assert torch.equal(eid.cpu(), ref_eid)                      # every token, not only the compared rows
+    assert torch.allclose(wt.cpu(), ref_wt, rtol=2e-5, atol=1e-9)
+    ref = oracle.moe_rows(x[rows], ref_eid[rows], ref_wt[rows], fetch, shared, 10.0)
+    assert rel_err(routed[rows.to(dev)], ref["routed"]) <= 2e-3
+    assert rel_err(out[rows.to(dev)], ref["out"]) <= 1e-2
+
+
+@pytest.mark.parametrize("S", [1, 8, 32, 64])
+def test_decode_batches_all_experts_resident(mods, oracle, dev, full_layer, S):
+    """The decode workloads of the benchmark (S tokens against all 384 experts); every row is compared."""
+    _compare(mods, oracle, dev, full_layer, S, torch.arange(S), seed=2000 + S, rotate=29 * S)
+
+
+def test_prefill_4096_ragged_groups(mods, oracle, dev, full_layer):
+    """The prefill workload: 4096 tokens, 24,576 pairs in ragged per-expert groups (Zipf routing); the expert indices of all tokens
+    and a seeded sample of 64 rows are compared."""
+    T = 4096
+    rows = torch.randperm(T, generator=torch.Generator().manual_seed(7))[:64].sort().values
+    _compare(mods, oracle, dev, full_layer, T, rows, seed=3000)

@@ -156,6 +156,30 @@ def test_fp4_gemm_tc_groups_and_shards(mods, oracle, dev, G, M):
         assert (y.cpu()[~mask] == 7.0).all()
 
 
+def test_grouped_fp4_shard_zero_out_with_permuted_output_rows(mods, oracle, dev):
+    """zero_out clears the rows the foreign pairs WRITE (pair_out), not the rows at their positions, and never a row beyond the
+    output: output rows = tokens here (fewer than pairs), several pairs of a token would share a row, so each pair gets its own
+    slot of a [T * topk] buffer addressed through pair_out."""
+    E, N, K, T, topk = 8, 256, 512, 5, 3
+    w, s, g = _experts(E, N, K, 321, 112, 128)
+    x = mods.quant.fake_quant_fp8((torch.randn(T, K, generator=g) * 2).to(torch.bfloat16), 32)
+    eid = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)])
+    order = torch.argsort(eid.flatten(), stable=True)
+    experts, counts = torch.unique(eid.flatten()[order], return_counts=True)
+    grp_start = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)]).int()
+    pair_tok, pair_out = (order // topk).int(), order.int()   # sorted position -> token row, -> original slot t * topk + j
+    P = T * topk
+    ref = oracle.fp4_pairs(x, w, s, eid.flatten()[order], pair_tok, pair_out, None, P)
+    local = ((eid.flatten() >= 2) & (eid.flatten() < 5))     # by original slot
+    for zero_out, fill in ((True, 0.0), (False, 7.0)):
+        out = torch.full((P, N), 7.0, device=dev)
+        y = mods.cukern.grouped_fp4(x.to(dev), w[2:5].to(dev), s[2:5].to(dev), experts.int().to(dev), grp_start.to(dev), None, pair_tok.to(dev), pair_out.to(dev),
+                                    None, P, shard_start=2, shard_n=3, zero_out=zero_out, out=out).cpu()
+        assert rel_err(y[local], ref[local]) < 2e-3
+        assert (y[~local] == fill).all()
+    assert mods.cukern.device_error(dev) == 0
+
+
 @pytest.mark.parametrize("M,topk", [(1, 6), (5, 6), (64, 6), (100, 6)])
 def test_grouped_fp4_gemm_scatter_add(mods, oracle, dev, M, topk):
     """dsv41/test_moe.py:21-36 at reduced size: out[row_out] += weight * a[row_in] @ W[expert]^T."""
@@ -203,7 +227,7 @@ def test_fp8_gemm_e8m0(mods, oracle, dev, M, N, K):
 
 
 @pytest.mark.parametrize("M", [1, 2, 4, 8])
-@pytest.mark.parametrize("N", [4096, 12288])
+@pytest.mark.parametrize("N", [4096, 12288, 18432])
 def test_fp8_gemv_f32_block_scales(mods, oracle, dev, M, N):
     """The 128x128 fp32-scaled format: weights N(0, 0.02) quantised per block with scale = blockmax/448."""
     K = 4096
@@ -216,6 +240,21 @@ def test_fp8_gemv_f32_block_scales(mods, oracle, dev, M, N):
     assert rel_err(y, ref) < 2e-3
     # the quantised matrix stays close to the fp32 one
     assert rel_err(ref, x.float() @ wf.T) < 0.1
+    W = mods.w8.W8(codes.to(dev), scale.to(dev))
+    assert rel_err(mods.w8.linear_w(x.to(dev), W), ref) < 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8])
+@pytest.mark.parametrize("N", [4096, 12288, 18432])
+def test_fp8_gemv_e8m0_block_scales_at_benchmark_shapes(mods, oracle, dev, M, N):
+    """The same N(0, 0.02) weights in the reference's own format (E8M0 per 32x32, scale 2^ceil(log2(blockmax/448))), K = 4096."""
+    K = 4096
+    g = torch.Generator().manual_seed(3 * N + M)
+    codes, scale = mods.synth.quantize_fp8_block(torch.randn(N, K, generator=g) * 0.02, "e8m0")
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    ref = oracle.fp8_gemm(x, codes, scale)
+    y = mods.cukern.fp8_gemm_tc(x.to(dev), codes.to(dev), scale.to(dev), out_dtype=torch.float32, permuted=False)
+    assert rel_err(y, ref) < 2e-3
     W = mods.w8.W8(codes.to(dev), scale.to(dev))
     assert rel_err(mods.w8.linear_w(x.to(dev), W), ref) < 1e-2
 

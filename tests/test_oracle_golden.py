@@ -142,6 +142,24 @@ def test_moe_layer_composition(oracle):
     assert torch.allclose(acc, r["routed"], rtol=1e-6, atol=1e-6 * r["routed"].abs().max().item())
 
 
+def test_moe_rows_equals_moe_layer(oracle):
+    """`moe_rows` (the layer for selected rows with the experts fetched on demand, used at the benchmark's 384-expert size) is the
+    same arithmetic as `moe_layer`, bit for bit, with and without a shard."""
+    g = torch.Generator().manual_seed(4)
+    E, D, I, T, topk = 8, 256, 256, 5, 3
+    r8 = lambda lo, hi, *shape: torch.randint(lo, hi, shape, dtype=torch.uint8, generator=g)
+    w13, s13, w2, s2 = r8(0, 256, E, 2 * I, D // 2), r8(118, 124, E, 2 * I, D // 32), r8(0, 256, E, D, I // 2), r8(118, 124, E, D, I // 32)
+    sh = (r8(0, 120, 2 * I, D), r8(115, 120, 2 * I // 32, D // 32), r8(0, 120, D, I), r8(115, 120, D // 32, I // 32))
+    x = torch.randn(T, D, generator=g).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g)
+    fetch = lambda ids: (w13[ids], s13[ids], w2[ids], s2[ids])
+    full = oracle.moe_layer(x, logits, None, w13, s13, w2, s2, sh, topk=topk, limit=10.0)
+    rows = oracle.moe_rows(x, full["eid"], full["wt"], fetch, sh, 10.0)
+    assert torch.equal(rows["out"], full["out"]) and torch.equal(rows["routed"], full["routed"])
+    part = oracle.moe_layer(x, logits, None, w13[2:5], s13[2:5], w2[2:5], s2[2:5], None, topk=topk, shard=(2, 3), n_experts=E)
+    assert torch.equal(oracle.moe_rows(x, full["eid"], full["wt"], fetch, None, 10.0, shard=(2, 3))["routed"], part["routed"])
+
+
 def test_hc_restatements_basic_properties():
     # dsv41/fused2.py:171-246, 505-558 restated on the CPU: identities that hold whatever the inputs
     import torch
