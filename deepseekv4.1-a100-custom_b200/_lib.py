@@ -29,7 +29,8 @@ class MoeArgs(ctypes.Structure):
                 ("has_shared", c_i), ("sh_w13", c_p), ("sh_s13", c_p), ("sh_w2", c_p), ("sh_s2", c_p),
                 ("shared_fmt", c_i), ("sh_s13_cols", c_i), ("sh_s2_cols", c_i), ("sh_permk", c_i), ("swiglu_limit", c_f),
                 ("out", c_p), ("routed_out", c_p), ("eid_out", c_p), ("wt_out", c_p), ("workspace", c_p), ("workspace_bytes", c_sz),
-                ("prof_start", c_p), ("prof_stop", c_p), ("engine", c_i), ("shared_out", c_p), ("x_ld", c_ll), ("logits_ld", c_ll), ("gate_w", c_p), ("xf", c_p), ("xf_ld", c_ll)]
+                ("prof_start", c_p), ("prof_stop", c_p), ("engine", c_i), ("shared_out", c_p), ("x_ld", c_ll), ("logits_ld", c_ll), ("gate_w", c_p), ("xf", c_p), ("xf_ld", c_ll),
+                ("s13_atoms", c_p), ("s2_atoms", c_p), ("sh_s13_atoms", c_p), ("sh_s2_atoms", c_p)]
 
 
 _SIGNATURES = {
@@ -57,6 +58,8 @@ _SIGNATURES = {
     "b200_hc_pre_norm_quant2": (c_i, [c_p, c_p, c_p, c_i, c_f, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
     "b200_hc_post2": (c_i, [c_p, c_p, c_p, c_ll, c_ll, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_p]),
     "b200_device_error": (c_i, [c_p, c_p]),
+    "b200_scale_atoms_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
+    "b200_scale_atoms": (c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p]),
 }
 
 _lib = None

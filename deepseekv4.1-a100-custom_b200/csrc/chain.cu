@@ -3,9 +3,12 @@
 // Layer = one routing kernel (router, bucketing of the (token, expert) pairs by expert, work list; for the streaming engine also
 // the input fake quantisation), then either the block-scaled tensor-core GEMMs (mxgemm.cu: one quantisation launch, gate/up GEMM and
 // down GEMM, each carrying the routed experts and the shared expert) or the weight-streaming GEMMs (skinny.cu), then a combine.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "skinny.cuh"
 #include "mxgemm.cuh"
+#include "wmgemm.cuh"
 #include "gate_gemm.cuh"
 #include "router.cuh"
 #include "b200_moe.h"
@@ -173,6 +176,218 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
         a.pair_tok[o] = p / a.topk;
         a.pair_out[o] = p;
         a.pair_w[o] = __ldcg(a.wt + p);
+    }
+}
+
+// ------------------------------------------------------------------ decode-sized batches (at most 64 tokens) on the weight-stream kernels
+// One block per token: FP8 quantisation of the token's activation kept in quantised form (e4m3 bytes + the E8M0 scale bytes written
+// straight into the 512-byte atoms the tensor cores read, see wmgemm.cu), and the router.  The last block to finish lists the
+// distinct experts of this shard that any token chose (one work each, in expert order) and fills, per work, a table over the tokens:
+// slot[w][t] = 1 + the top-k slot of expert w in token t's selection (0: t did not choose it), wtab[w][t] = its routing weight.
+// Nothing is sorted or gathered: every work multiplies its expert with all tokens and the epilogues keep the chosen pairs.
+struct DqRouteArgs {
+    int tokens, E, topk, dim, NT;
+    const float* logits_f32;
+    const __nv_bfloat16* logits_bf16;
+    const float* bias;
+    float temp, route_scale;
+    int mode, norm;
+    const __nv_bfloat16* x;
+    long long x_ld, logits_ld;
+    int logit_parts;
+    long long logit_part_stride;
+    int shard_start, shard_n;
+    int* eid;
+    float* wt;
+    uint8_t* x8;        // [NT][dim]
+    uint8_t* x_atoms;   // [dim / 128][512]
+    int* work;
+    int* n_work;
+    uint8_t* slot;      // [works][NT]
+    int* pair_work;     // [tokens * topk]: work of the pair's expert, -1 when the expert is not in this shard
+    unsigned int* counter;
+    int* flags;         // flag words of the split-k exchange of the two GEMM launches that follow: cleared here
+    int n_flags;
+};
+
+__global__ void __launch_bounds__(ROUTE_THREADS) dq_route_kernel(const DqRouteArgs a) {
+    __shared__ float s_val[ROUTE_MAX_EXPERTS], s_key[ROUTE_MAX_EXPERTS];
+    __shared__ float s_raw[ROUTE_MAX_EXPERTS];
+    __shared__ int s_widx[ROUTE_MAX_EXPERTS];
+    __shared__ int s_wtot[ROUTE_THREADS / 32];
+    __shared__ int is_last;
+    const int tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    if (blockIdx.x == 0)
+        for (int i = tid; i < a.n_flags; i += ROUTE_THREADS) a.flags[i] = 0;
+
+    const int groups = a.dim >> 5;
+    for (int gi = tid; gi < groups; gi += ROUTE_THREADS) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.x + (long)tok * a.x_ld + gi * 32);
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = __ldg(src + j);
+        const uint32_t* w = reinterpret_cast<const uint32_t*>(v);
+        float f[32], amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            f[2 * j] = bf16_bits_to_f32(w[j] & 0xFFFFu);
+            f[2 * j + 1] = bf16_bits_to_f32(w[j] >> 16);
+            amax = fmaxf(amax, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
+        }
+        const float sc = fp8_group_scale_bf16(amax);  // the inputs are bf16 values
+        const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
+        const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t q = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float qv = fminf(fmaxf(f[4 * j + e] * inv, -448.f), 448.f);
+                q |= (uint32_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3) << (8 * e);
+            }
+            o[j] = q;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(a.x8 + (long)tok * a.dim + gi * 32);
+        dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        a.x_atoms[(size_t)(gi >> 2) * 512 + (tok & 31) * 16 + (tok >> 5) * 4 + (gi & 3)] = (uint8_t)sb;
+    }
+    if (a.logit_parts > 0) {
+        const float* base = a.logits_f32 + (long)tok * a.E;
+        for (int e = tid; e < a.E; e += ROUTE_THREADS) {
+            float v = 0.f;
+#pragma unroll 4
+            for (int p = 0; p < a.logit_parts; ++p) v += __ldg(base + (long long)p * a.logit_part_stride + e);
+            s_raw[e] = v;
+        }
+        __syncthreads();
+    }
+    if (warp == 0) {
+        const float* row_f32 = a.logit_parts > 0 ? s_raw : (a.logits_f32 ? a.logits_f32 + (long)tok * a.logits_ld : nullptr);
+        gate_topk_warp(row_f32, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E, a.temp, a.topk, a.route_scale, a.mode, a.norm,
+                       a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = (atomicInc(a.counter, gridDim.x - 1) == gridDim.x - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+
+    const int P = a.tokens * a.topk, E = a.E;
+    for (int e = tid; e < E; e += ROUTE_THREADS) s_widx[e] = 0;
+    __syncthreads();
+    for (int p = tid; p < P; p += ROUTE_THREADS) {
+        const int e = __ldcg(a.eid + p);
+        if (e >= a.shard_start && e < a.shard_start + a.shard_n) s_widx[e] = 1;  // every writer stores the same value
+    }
+    __syncthreads();
+    const int per = (E + ROUTE_THREADS - 1) / ROUTE_THREADS;
+    int loc = 0;
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < E) loc += s_widx[e];
+    }
+    int inc = loc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += v;
+    }
+    if (lane == 31) s_wtot[warp] = inc;
+    __syncthreads();
+    int run = inc - loc, total = 0;
+    for (int w = 0; w < ROUTE_THREADS / 32; ++w) {
+        if (w < warp) run += s_wtot[w];
+        total += s_wtot[w];
+    }
+    if (tid == 0) *a.n_work = total;
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < E) {
+            if (s_widx[e]) {
+                a.work[run] = e - a.shard_start;
+                s_widx[e] = run++;
+            } else {
+                s_widx[e] = -1;
+            }
+        }
+    }
+    uint32_t* slot32 = reinterpret_cast<uint32_t*>(a.slot);
+    for (int i = tid; i < total * (a.NT >> 2); i += ROUTE_THREADS) slot32[i] = 0;
+    __syncthreads();
+    for (int p = tid; p < P; p += ROUTE_THREADS) {
+        const int e = __ldcg(a.eid + p);
+        if (e < a.shard_start || e >= a.shard_start + a.shard_n) { a.pair_work[p] = -1; continue; }
+        const int w = s_widx[e], t = p / a.topk, j = p - t * a.topk;
+        a.slot[(size_t)w * a.NT + t] = (uint8_t)(j + 1);
+        a.pair_work[p] = w;
+    }
+}
+
+// SwiGLU (+ routing weight) + FP8 quantisation between the two GEMMs of a decode-sized batch (dsv41/fused.py:285-306): one block per
+// (token, expert) pair and one per token for the shared expert; a warp per group of 32 columns.  Reads the fp32 gate | up rows the first
+// GEMM stored, writes e4m3 bytes into the rows the second GEMM reads (row = work * NT + token) and the E8M0 scale bytes straight into
+// the 512-byte atoms its tensor cores take (wmgemm.cu).
+struct DqSwigluArgs {
+    const float* gu;       // [pairs][2 inter]
+    const float* gus;      // [tokens][2 inter] (shared expert; nullptr: none)
+    int pairs, tokens, topk, inter, NT;
+    const float* wt;       // [pairs]
+    const int* pair_work;  // [pairs]
+    float limit;
+    uint8_t *h8, *h_atoms, *hs8, *hs_atoms;
+};
+
+__global__ void __launch_bounds__(256) dq_swiglu_kernel(const DqSwigluArgs a) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, I = a.inter;
+    const float* src;
+    uint8_t *out, *atoms;
+    float w = 1.f;
+    int t, round_gu = 0;
+    if (b < a.pairs) {
+        const int wk = __ldg(a.pair_work + b);
+        if (wk < 0) return;
+        t = b / a.topk;
+        w = __ldg(a.wt + b);
+        src = a.gu + (size_t)b * 2 * I;
+        out = a.h8 + ((size_t)wk * a.NT + t) * I;
+        atoms = a.h_atoms + (size_t)wk * (I >> 7) * 512;
+    } else {
+        t = b - a.pairs;
+        src = a.gus + (size_t)t * 2 * I;
+        out = a.hs8 + (size_t)t * I;
+        atoms = a.hs_atoms;
+        round_gu = 1;  // the shared expert's gate / up values pass through bf16 (dsv41/model.py:1635-1638)
+    }
+    for (int g0 = warp; g0 < (I >> 5); g0 += 32) {  // four groups per warp and pass: independent chains in flight
+        float h[4], amax[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int g = g0 + 8 * u;
+            float gt = 0.f, up = 0.f;
+            if (g < (I >> 5)) { gt = __ldcg(src + g * 32 + lane); up = __ldcg(src + I + g * 32 + lane); }
+            if (round_gu) { gt = round_bf16(gt); up = round_bf16(up); }
+            h[u] = swiglu_bf16(gt, up, w, a.limit);
+            amax[u] = fabsf(h[u]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int g = g0 + 8 * u;
+            if (g >= (I >> 5)) continue;
+            const uint32_t sb = (f32_as_u32(fp8_group_scale_bf16(amax[u])) >> 23) & 0xFFu;
+            const float qv = fminf(fmaxf(h[u] * u32_as_f32((254u - sb) << 23), -448.f), 448.f);
+            out[g * 32 + lane] = (uint8_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
+            if (lane == 0) atoms[(size_t)(g >> 2) * 512 + (t & 31) * 16 + (t >> 5) * 4 + (g & 3)] = (uint8_t)sb;
+        }
     }
 }
 
@@ -354,7 +569,17 @@ struct MoeWs {
     int* cnt; int* cursor; __nv_bfloat16* hq; __nv_bfloat16* hs; float* y2; float* acc; __nv_bfloat16* ys;
     uint8_t *x8s, *xsfs, *x8t, *xsft, *hq8, *hsf, *hs8, *hssf;
     float* logit_parts;  // k-split partial logits of the fused router projection: [GATE_MAX_SPLITS or fewer][T][E]
+    // decode-sized batches on the weight-stream kernels (wmgemm.cu)
+    uint8_t *dq_x_atoms, *dq_h8, *dq_h_atoms, *dq_hs_atoms, *dq_slot;
+    float *dq_gu, *dq_gus, *dq_partial;
+    int *dq_work, *dq_pair_work, *dq_flags;
 };
+
+constexpr int DQ_MAX_TOKENS = WM_NT_MAX;   // batches up to this size take the weight-stream kernels
+constexpr int DQ_FUSE_SWIGLU_TOKENS = 16;  // up to this many tokens SwiGLU runs in the gate/up GEMM's epilogue
+constexpr int DQ_MAX_CTAS = 192;           // CTAs the split-k exchange buffers are sized for
+static int dq_nt(int T) { return T <= 16 ? 16 : (T <= 32 ? 32 : 64); }
+static size_t dq_max_works(size_t P) { return P < (size_t)ROUTE_MAX_EXPERTS ? P : (size_t)ROUTE_MAX_EXPERTS; }
 
 static bool carve_moe(Carver& cv, MoeWs& w, int T, int topk, int D, int I) {
     const size_t P = (size_t)T * topk;
@@ -390,6 +615,19 @@ static bool carve_moe(Carver& cv, MoeWs& w, int T, int topk, int D, int I) {
         if (need > lp) lp = need;
     }
     w.logit_parts = cv.take<float>(lp);
+    const bool dq = T > 0 && T <= DQ_MAX_TOKENS && D % 128 == 0 && I % 128 == 0;
+    const size_t NT = dq_nt(T), MW = dq_max_works(P);
+    w.dq_x_atoms = cv.take<uint8_t>(dq ? (size_t)(D / 128) * 512 : 0);
+    w.dq_h8 = cv.take<uint8_t>(dq ? (MW * NT + 128) * I : 0);          // SwiGLU outputs of work w: rows [w * NT, w * NT + NT)
+    w.dq_h_atoms = cv.take<uint8_t>(dq ? MW * (I / 128) * 512 : 0);
+    w.dq_hs_atoms = cv.take<uint8_t>(dq ? (size_t)(I / 128) * 512 : 0);
+    w.dq_slot = cv.take<uint8_t>(dq ? MW * NT : 0);
+    w.dq_gu = cv.take<float>(dq ? P * 2 * I : 0);                       // gate | up of every (token, expert) pair, row = token * topk + slot
+    w.dq_gus = cv.take<float>(dq ? (size_t)T * 2 * I : 0);              // gate | up of the shared expert
+    w.dq_work = cv.take<int>(dq ? MW : 0);
+    w.dq_pair_work = cv.take<int>(dq ? P : 0);
+    w.dq_partial = cv.take<float>(dq ? (size_t)DQ_MAX_CTAS * (WM_PARTIAL_BYTES / sizeof(float)) : 0);
+    w.dq_flags = cv.take<int>(dq ? 2 * DQ_MAX_CTAS : 0);
     return cv.ok;
 }
 
@@ -434,6 +672,92 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     __nv_bfloat16* const ys_buf = m->shared_out ? (__nv_bfloat16*)m->shared_out : w.ys;  // the shared expert's result
     cudaError_t ce;
     int rc;
+
+    // ---- decode-sized batches: the weight-stream kernels (wmgemm.cu), 4 launches: route + quantise, gate/up, down, combine
+    const bool dq_shared_ok = !m->has_shared || (m->sh_s13_atoms && m->sh_s2_atoms);
+    if (T <= DQ_MAX_TOKENS && mx_ok && m->engine != 1 && m->s13_atoms && m->s2_atoms && dq_shared_ok && !m->x_is_quantized) {
+        const int NT = dq_nt(T);
+        DqRouteArgs r{};
+        r.tokens = T; r.E = E; r.topk = topk; r.dim = D; r.NT = NT;
+        r.logits_f32 = m->logits_is_bf16 ? nullptr : (const float*)m->logits;
+        r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
+        if (!m->logits) {
+            const int splits = gate_gemm_splits(T, E, D);
+            if ((rc = gate_gemm((const float*)m->xf, m->xf_ld > 0 ? m->xf_ld : D, m->xf ? nullptr : (const __nv_bfloat16*)m->x, m->x_ld > 0 ? m->x_ld : D,
+                                (const float*)m->gate_w, T, E, D, splits, w.logit_parts, stream)))
+                return rc;
+            r.logits_f32 = w.logit_parts; r.logits_bf16 = nullptr;
+            r.logit_parts = splits; r.logit_part_stride = (long long)T * E;
+        }
+        r.bias = m->gate_bias; r.temp = m->temp; r.route_scale = m->route_scale; r.mode = m->score_mode; r.norm = m->norm;
+        r.x = (const __nv_bfloat16*)m->x; r.x_ld = m->x_ld > 0 ? m->x_ld : D; r.logits_ld = (m->logits && m->logits_ld > 0) ? m->logits_ld : E;
+        r.shard_start = m->shard_start; r.shard_n = shard_n;
+        r.eid = w.eid; r.wt = w.wt; r.x8 = w.x8t; r.x_atoms = w.dq_x_atoms; r.work = w.dq_work; r.n_work = w.n_work; r.slot = w.dq_slot; r.pair_work = w.dq_pair_work;
+        r.counter = w.counter; r.flags = w.dq_flags; r.n_flags = 2 * DQ_MAX_CTAS;
+        if ((ce = cudaMemsetAsync(w.counter, 0, sizeof(unsigned int), stream)) != cudaSuccess) return (int)ce;
+        dq_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
+        B200_CHECK_LAUNCH();
+        const long long MW = (long long)dq_max_works((size_t)P);
+        // SwiGLU + quantisation: in the epilogue of the gate/up GEMM for the smallest batches (a handful of rows per tile), in a kernel of
+        // its own between the GEMMs otherwise (a hot expert's tile carries dozens of rows, which would hold up the CTA that gets it)
+        const bool fuse_swiglu = T <= DQ_FUSE_SWIGLU_TOKENS;
+        WmArgs g1{};
+        g1.n_prob = shared ? 2 : 1;
+        g1.K = D; g1.NT = NT; g1.dual = 1; g1.inter = I; g1.limit = m->swiglu_limit;
+        g1.split_k = 1; g1.partial = w.dq_partial; g1.flags = w.dq_flags; g1.flag_value = 1; g1.max_ctas = DQ_MAX_CTAS;
+        {
+            WmProb& q = g1.p[0];
+            q.w = m->w13; q.w_estride = (long long)2 * I * (D / 2); q.n_experts = shard_n; q.a_fmt = MX_A_E2M1;
+            q.w_atoms = (const uint8_t*)m->s13_atoms; q.atoms_estride = (long long)scale_atoms_bytes(1, 2 * I, D, 1);
+            q.N = 2 * I; q.x8 = w.x8t; q.x8_rows = T + 128; q.x_atoms = w.dq_x_atoms; q.x_per_work = 0;
+            q.work = w.dq_work; q.n_work = w.n_work; q.slot = w.dq_slot; q.tokens = T; q.topk = topk;
+            if (fuse_swiglu) { q.epi = WM_EPI_SWIGLU_Q8; q.out = w.dq_h8; q.out_ld = I; q.out_atoms = w.dq_h_atoms; q.pair_w = w.wt; }
+            else { q.epi = WM_EPI_STORE_F32; q.out = w.dq_gu; q.out_ld = 2 * I; }
+        }
+        if (shared) {
+            WmProb& q = g1.p[1];
+            q.w = m->sh_w13; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
+            q.w_atoms = (const uint8_t*)m->sh_s13_atoms; q.N = 2 * I; q.x8 = w.x8t; q.x8_rows = T + 128; q.x_atoms = w.dq_x_atoms; q.x_per_work = 0;
+            q.work = nullptr; q.n_work_host = 1; q.tokens = T; q.topk = topk;
+            if (fuse_swiglu) { q.epi = WM_EPI_SWIGLU_Q8; q.out = w.hs8; q.out_ld = I; q.out_atoms = w.dq_hs_atoms; q.round_gu_bf16 = 1; }
+            else { q.epi = WM_EPI_STORE_F32; q.out = w.dq_gus; q.out_ld = 2 * I; }
+        }
+        if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
+        if ((rc = wm_launch(g1, stream))) return rc;
+        if (m->prof_stop && (ce = cudaEventRecord((cudaEvent_t)m->prof_stop, stream)) != cudaSuccess) return (int)ce;
+        DqSwigluArgs sq{};
+        sq.gu = w.dq_gu; sq.gus = shared ? w.dq_gus : nullptr; sq.pairs = (int)P; sq.tokens = T; sq.topk = topk; sq.inter = I; sq.NT = NT;
+        sq.wt = w.wt; sq.pair_work = w.dq_pair_work; sq.limit = m->swiglu_limit;
+        sq.h8 = w.dq_h8; sq.h_atoms = w.dq_h_atoms; sq.hs8 = w.hs8; sq.hs_atoms = w.dq_hs_atoms;
+        if (!fuse_swiglu && (ce = launch_pdl(dq_swiglu_kernel, dim3((unsigned)(P + (shared ? T : 0))), dim3(256), 0, stream, sq)) != cudaSuccess) return (int)ce;
+        WmArgs g2{};
+        g2.n_prob = shared ? 2 : 1;
+        g2.K = I; g2.NT = NT; g2.dual = 0;
+        g2.split_k = 1; g2.partial = w.dq_partial; g2.flags = w.dq_flags + DQ_MAX_CTAS; g2.flag_value = 1; g2.max_ctas = DQ_MAX_CTAS;
+        {
+            WmProb& q = g2.p[0];
+            q.w = m->w2; q.w_estride = (long long)D * (I / 2); q.n_experts = shard_n; q.a_fmt = MX_A_E2M1;
+            q.w_atoms = (const uint8_t*)m->s2_atoms; q.atoms_estride = (long long)scale_atoms_bytes(1, D, I, 0);
+            q.N = D; q.x8 = w.dq_h8; q.x8_rows = MW * NT + 128; q.x_atoms = w.dq_h_atoms; q.x_per_work = 1;
+            q.work = w.dq_work; q.n_work = w.n_work; q.slot = w.dq_slot; q.tokens = T; q.topk = topk;
+            q.epi = WM_EPI_STORE_F32; q.out = w.y2; q.out_ld = D;
+        }
+        if (shared) {
+            WmProb& q = g2.p[1];
+            q.w = m->sh_w2; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
+            q.w_atoms = (const uint8_t*)m->sh_s2_atoms; q.N = D; q.x8 = w.hs8; q.x8_rows = T + 128; q.x_atoms = w.dq_hs_atoms; q.x_per_work = 0;
+            q.work = nullptr; q.n_work_host = 1; q.tokens = T; q.topk = topk;
+            q.epi = WM_EPI_STORE_BF16; q.out = ys_buf; q.out_ld = D;
+        }
+        if ((rc = wm_launch(g2, stream))) return rc;
+        const long n = (long)T * D;
+        if ((ce = launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.y2, (const int*)w.eid,
+                             (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, m->routed_out, T, topk, D, m->shard_start, shard_n)) != cudaSuccess)
+            return (int)ce;
+        if (m->eid_out && (ce = cudaMemcpyAsync(m->eid_out, w.eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
+        if (m->wt_out && (ce = cudaMemcpyAsync(m->wt_out, w.wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
+        return 0;
+    }
 
     // ---- routing (+ bf16 fake quantisation of the input for the streaming engine)
     RouteArgs r{};
@@ -587,6 +911,14 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     return 0;
 }
 
+// ------------------------------------------------------------------ load-time re-layout of the scales
+extern "C" size_t b200_scale_atoms_bytes(int n_experts, int N, int K, int dual) { return scale_atoms_bytes(n_experts, N, K, dual); }
+
+extern "C" int b200_scale_atoms(const void* s, int fmt, int s_cols, int n_experts, int N, int K, int dual, void* dst, cudaStream_t stream) {
+    if (fmt != SK_FMT_FP4_E8M0 && fmt != SK_FMT_FP8_E8M0) return ERR_UNSUPPORTED;
+    return scale_atoms((const uint8_t*)s, fmt == SK_FMT_FP8_E8M0 ? 5 : 0, s_cols, n_experts, N, K, dual, (uint8_t*)dst, stream);
+}
+
 // ------------------------------------------------------------------ block-scaled tensor-core GEMM, stand-alone entry points
 extern "C" int b200_mx_quantize_rows(const void* x, long long x_ld, const int* src_row, int rows, int K, void* q8, void* sf, cudaStream_t stream) {
     return mx_quantize_rows((const __nv_bfloat16*)x, x_ld, src_row, rows, K, (uint8_t*)q8, (uint8_t*)sf, stream);
@@ -598,7 +930,10 @@ extern "C" int b200_device_error(int* code, cudaStream_t stream) {
     int rc = mx_device_error(&mx, stream);  // synchronises the stream
     if (rc) return rc;
     if ((rc = skinny_device_error(&sk))) return rc;
-    *code = mx ? mx : (sk ? 1000 + sk : 0);  // tensor-core kernels report 11..41, the streaming kernels 1001..1091
+    int wm = 0;
+    if ((rc = wm_device_error(&wm))) return rc;
+    // prefill tensor-core kernel 11..41, streaming kernels 1001..1091, decode weight-stream kernel 2011..2042
+    *code = mx ? mx : (sk ? 1000 + sk : (wm ? 2000 + wm : 0));
     return 0;
 }
 

@@ -219,6 +219,26 @@ def mx_grouped(w, s, x8, xsf, grp_expert, grp_start, grp_count, pair_out, pair_w
     return (out, out_sf) if epi == 1 else out
 
 
+def scale_atoms(s: torch.Tensor, n_rows: int, K: int, dual: bool) -> torch.Tensor:
+    """Load-time re-layout of E8M0 scales into the 512-byte atoms the tensor cores read (b200_scale_atoms, include/b200_moe.h).
+    s uint8 [E, N, K/32] (expert scales, one row of scales per weight row) or [ceil(N/32), K/32] (dense FP8 format, 32x32 blocks);
+    dual: a gate|up matrix (N = 2 * inter).  Returns uint8 [E, tiles, K/128, 2, 512]."""
+    dev = L.require_cuda(s)
+    assert s.dtype == torch.uint8 and s.is_contiguous() and K % 128 == 0
+    lib = L.lib()
+    if s.dim() == 3:
+        E, fmt = s.shape[0], L.FMT_FP4_E8M0
+        assert s.shape[1] == n_rows and s.shape[2] >= K // 32
+    else:
+        E, fmt = 1, L.FMT_FP8_E8M0
+        assert s.shape[0] == (n_rows + 31) // 32 and s.shape[1] >= K // 32
+    nbytes = lib.b200_scale_atoms_bytes(E, n_rows, K, int(dual))
+    out = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        L.check(lib.b200_scale_atoms(L.ptr(s), fmt, s.shape[-1], E, n_rows, K, int(dual), L.ptr(out), L.stream_of(dev)), "b200_scale_atoms")
+    return out.view(E, -1, K // 128, 2, 512)
+
+
 def device_error(device) -> int:
     """Synchronise the device's current stream and return (then clear) the device error word (0 = no bounded wait gave up)."""
     import ctypes

@@ -52,6 +52,15 @@ class MoELayer:
         if self._mx_ok and engine != 1 and sh_w13 is not None:
             from .w8 import unpermute_k
             self._sh_nat = (unpermute_k(sh_w13.w8), unpermute_k(sh_w2.w8))
+        # load-time re-layout of the scales (1/16 of the weight bytes): the decode kernels read them as ready-made tensor-core
+        # scale atoms by bulk copy instead of gathering bytes in checkpoint order
+        self._atoms = None
+        if self._mx_ok and engine != 1:
+            from . import cukern
+            at = [cukern.scale_atoms(self.s13, 2 * self.inter, self.dim, True), cukern.scale_atoms(self.s2, self.dim, self.inter, False)]
+            if sh_w13 is not None:
+                at += [cukern.scale_atoms(sh_w13.s8, 2 * self.inter, self.dim, True), cukern.scale_atoms(sh_w2.s8, self.dim, self.inter, False)]
+            self._atoms = at
 
     def _use_mx(self, tokens: int) -> bool:
         return self.engine == 2 or (self.engine == 0 and self._mx_ok and tokens > 0)
@@ -61,9 +70,13 @@ class MoELayer:
         """Kernels of this library one forward() launches for `tokens` tokens."""
         if tokens * self.topk > 4096:
             return 8   # route, histogram, scan, scatter, quantise, gate/up GEMM, down GEMM, finalise
+        if self._use_mx(tokens) and self._atoms is not None and tokens <= 64:
+            return 4 if tokens <= 16 else 5   # route + quantise, gate/up GEMM, (SwiGLU + quantise,) down GEMM, combine
         return 5 if self._use_mx(tokens) else (6 if self.sh_w13 is not None else 4)
 
     def dominant_kernel(self, tokens: int) -> str:
+        if self._use_mx(tokens) and self._atoms is not None and tokens <= 64:
+            return "wm_gemm_kernel (gate/up weight stream of the routed experts and the shared expert, weight rows on the M side of tcgen05 kind::mxf8f6f4 tiles, k range cut evenly over the SMs, + SwiGLU + FP8 quant)"
         if self._use_mx(tokens):
             return "mx_gemm_kernel (gate/up weight stream of the routed experts and the shared expert on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)"
         return "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"
@@ -145,6 +158,10 @@ class MoELayer:
             a.swiglu_limit = float(self.swiglu_limit)
             a.engine = 2 if mx else 1
             a.gate_w = self.gate_w.data_ptr() if self.gate_w is not None else None
+            if mx and self._atoms is not None:
+                a.s13_atoms, a.s2_atoms = self._atoms[0].data_ptr(), self._atoms[1].data_ptr()
+                if len(self._atoms) == 4:
+                    a.sh_s13_atoms, a.sh_s2_atoms = self._atoms[2].data_ptr(), self._atoms[3].data_ptr()
             nbytes = lib.b200_moe_workspace_bytes(T, self.topk, self.dim, self.inter)
             cached = self._args[key] = (a, nbytes)
         a, nbytes = cached

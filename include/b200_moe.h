@@ -179,10 +179,24 @@ typedef struct b200_moe_args {
     const void* gate_w;
     const void* xf;
     long long xf_ld;
+    /* optional: the E8M0 scales re-laid-out once, at load time, into the 512-byte atoms the tensor cores read (b200_scale_atoms
+     * below): s13_atoms of s13 (dual = 1), s2_atoms of s2 (dual = 0), sh_s13_atoms / sh_s2_atoms of the shared expert's 32x32 scales.
+     * With all of them given (and E8M0 formats), batches of up to 64 tokens run on the weight-stream kernels: 4 launches per call, the
+     * k range of every launch cut evenly over the SMs.  NULL: the kernels that read the scales in checkpoint order are used. */
+    const void *s13_atoms, *s2_atoms, *sh_s13_atoms, *sh_s2_atoms;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);
 int b200_moe_forward(const b200_moe_args* args, cudaStream_t stream);
+
+/* ---- load-time re-layout of E8M0 scales (the optional re-layout of the expert loader; the reference keeps checkpoint order,
+ * dsv41/load.py:237-249, and gathers scale bytes in every kernel).  s: bytes [n_experts][N][K/32] (fmt B200_FMT_FP4_E8M0, s_cols = K/32)
+ * or [ceil(N/32)][s_cols] (fmt B200_FMT_FP8_E8M0, n_experts = 1); dst: b200_scale_atoms_bytes(...) bytes, 16-byte aligned, laid out
+ * [expert][tile of 256 rows][K/128][2][512]: byte (r % 32) * 16 + (r / 32) * 4 + g of an atom = scale of row r (of the 128 of its row
+ * block), 32-group g of the 128-wide k block.  dual = 1 for a gate|up matrix (N = 2 * inter): tile t = gate rows 128 t .. and up rows
+ * inter + 128 t ..; dual = 0: rows 256 t ...  K % 128 == 0. */
+size_t b200_scale_atoms_bytes(int n_experts, int N, int K, int dual);
+int b200_scale_atoms(const void* s, int fmt, int s_cols, int n_experts, int N, int K, int dual, void* dst, cudaStream_t stream);
 
 /* ---- FP8 quantisation of activation rows kept in quantised form: q8 e4m3 [rows, K], sf E8M0 bytes [rows, K/32], the
  * values of quant_fp8 (dsv41/quant.py:57-64).  src_row int32 [rows] gathers input rows (NULL = identity). */
