@@ -30,7 +30,7 @@ class MoeArgs(ctypes.Structure):
                 ("shared_fmt", c_i), ("sh_s13_cols", c_i), ("sh_s2_cols", c_i), ("sh_permk", c_i), ("swiglu_limit", c_f),
                 ("out", c_p), ("routed_out", c_p), ("eid_out", c_p), ("wt_out", c_p), ("workspace", c_p), ("workspace_bytes", c_sz),
                 ("prof_start", c_p), ("prof_stop", c_p), ("engine", c_i), ("shared_out", c_p), ("x_ld", c_ll), ("logits_ld", c_ll), ("gate_w", c_p), ("xf", c_p), ("xf_ld", c_ll),
-                ("s13_atoms", c_p), ("s2_atoms", c_p), ("sh_s13_atoms", c_p), ("sh_s2_atoms", c_p)]
+                ("s13_atoms", c_p), ("s2_atoms", c_p), ("sh_s13_atoms", c_p), ("sh_s2_atoms", c_p), ("eid_in", c_p), ("wt_in", c_p)]
 
 
 _SIGNATURES = {
@@ -58,6 +58,19 @@ _SIGNATURES = {
     "b200_hc_pre_norm_quant2": (c_i, [c_p, c_p, c_p, c_i, c_f, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
     "b200_hc_post2": (c_i, [c_p, c_p, c_p, c_ll, c_ll, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_p]),
     "b200_device_error": (c_i, [c_p, c_p]),
+    "b200_p2p_copy": (c_i, [c_p, c_p, c_ll, c_p]),
+    "b200_p2p_copy_row": (c_i, [c_p, c_p, c_p, c_ll, c_i, c_ll, c_p, c_p]),
+    "b200_p2p_signal": (c_i, [c_p, c_i, c_p, c_p]),
+    "b200_p2p_wait": (c_i, [c_p, c_i, c_p, c_p, c_p]),
+    "b200_p2p_seq_bump": (c_i, [c_p, c_p]),
+    "b200_p2p_multicast": (c_i, [c_p, c_i, c_p, c_ll, c_p, c_p, c_p, c_p]),
+    "b200_p2p_stamp": (c_i, [c_p, c_p]),
+    "b200_memcpy_async": (c_i, [c_p, c_p, c_ll, c_p]),
+    "b200_set_wait_limit_ns": (c_i, [ctypes.c_ulonglong]),
+    "b200_group_pairs_max_tiles": (c_i, [c_i, c_i, c_i]),
+    "b200_group_pairs_workspace_bytes": (c_sz, [c_i]),
+    "b200_group_pairs": (c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
+    "b200_regroup_pairs": (c_i, [c_p, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_p]),
     "b200_scale_atoms_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "b200_scale_atoms": (c_i, [c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_p]),
 }

@@ -15,6 +15,8 @@
 
 namespace b200 {
 
+int p2p_device_error(int* out);  // p2p.cu
+
 constexpr int ROUTE_THREADS = 128;
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
@@ -199,6 +201,8 @@ struct DqRouteArgs {
     int shard_start, shard_n;
     int* eid;
     float* wt;
+    const int* eid_in;  // routing decided by the caller (then no router runs): [tokens][topk], with wt_in
+    const float* wt_in;
     uint8_t* x8;        // [NT][dim]
     uint8_t* x_atoms;   // [dim / 128][512]
     int* work;
@@ -264,7 +268,12 @@ __global__ void __launch_bounds__(ROUTE_THREADS) dq_route_kernel(const DqRouteAr
         }
         __syncthreads();
     }
-    if (warp == 0) {
+    if (a.eid_in) {
+        if (tid < a.topk) {
+            a.eid[(long)tok * a.topk + tid] = __ldg(a.eid_in + (long)tok * a.topk + tid);
+            a.wt[(long)tok * a.topk + tid] = __ldg(a.wt_in + (long)tok * a.topk + tid);
+        }
+    } else if (warp == 0) {
         const float* row_f32 = a.logit_parts > 0 ? s_raw : (a.logits_f32 ? a.logits_f32 + (long)tok * a.logits_ld : nullptr);
         gate_topk_warp(row_f32, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E, a.temp, a.topk, a.route_scale, a.mode, a.norm,
                        a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
@@ -644,7 +653,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->tokens < 0 || m->topk < 1 || m->n_experts < 1 || m->dim < 1 || m->inter < 1) return ERR_BAD_ARG;
     if ((m->x_ld > 0 && m->x_ld < m->dim) || (m->logits_ld > 0 && m->logits_ld < m->n_experts)) return ERR_BAD_ARG;
     if (m->tokens == 0) return 0;  // an empty batch is not an error; its (empty) buffers may be null
-    if ((!m->logits && !m->gate_w) || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
+    if (m->eid_in && (!m->wt_in || m->tokens > DQ_MAX_TOKENS || !m->s13_atoms)) return ERR_UNSUPPORTED;  // given routing: decode-sized batches only
+    if ((!m->logits && !m->gate_w && !m->eid_in) || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
     if (m->has_shared && (!m->sh_w13 || !m->sh_s13 || !m->sh_w2 || !m->sh_s2)) return ERR_BAD_ARG;
     const int T = m->tokens, topk = m->topk, D = m->dim, I = m->inter, E = m->n_experts;
     const long P = (long)T * topk;
@@ -681,7 +691,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         r.tokens = T; r.E = E; r.topk = topk; r.dim = D; r.NT = NT;
         r.logits_f32 = m->logits_is_bf16 ? nullptr : (const float*)m->logits;
         r.logits_bf16 = m->logits_is_bf16 ? (const __nv_bfloat16*)m->logits : nullptr;
-        if (!m->logits) {
+        r.eid_in = m->eid_in; r.wt_in = m->wt_in;
+        if (!m->logits && !m->eid_in) {
             const int splits = gate_gemm_splits(T, E, D);
             if ((rc = gate_gemm((const float*)m->xf, m->xf_ld > 0 ? m->xf_ld : D, m->xf ? nullptr : (const __nv_bfloat16*)m->x, m->x_ld > 0 ? m->x_ld : D,
                                 (const float*)m->gate_w, T, E, D, splits, w.logit_parts, stream)))
@@ -930,10 +941,11 @@ extern "C" int b200_device_error(int* code, cudaStream_t stream) {
     int rc = mx_device_error(&mx, stream);  // synchronises the stream
     if (rc) return rc;
     if ((rc = skinny_device_error(&sk))) return rc;
-    int wm = 0;
+    int wm = 0, pp = 0;
     if ((rc = wm_device_error(&wm))) return rc;
-    // prefill tensor-core kernel 11..41, streaming kernels 1001..1091, decode weight-stream kernel 2011..2042
-    *code = mx ? mx : (sk ? 1000 + sk : (wm ? 2000 + wm : 0));
+    if ((rc = p2p_device_error(&pp))) return rc;
+    // prefill tensor-core kernel 11..41, streaming kernels 1001..1091, decode weight-stream kernel 2011..2042, messaging waits 3001..3002
+    *code = mx ? mx : (sk ? 1000 + sk : (wm ? 2000 + wm : (pp ? 3000 + pp : 0)));
     return 0;
 }
 

@@ -148,17 +148,122 @@ def fp8_gemm_tc(x: torch.Tensor, w8: torch.Tensor, s8: torch.Tensor, group_cols:
     return _fp8(x, w8, s8, permuted, out_dtype, out)
 
 
-# --------------------------------------------------------------------------- expert-parallel helpers
+# --------------------------------------------------------------------------- device-side GPU messaging (expert parallelism)
+# Same names and arguments as dsv41/cukern.py:348-434.  Every launcher enqueues on the current stream of `device`; destinations and
+# flags may live on another GPU as long as this process can address them.  p2p_wait / p2p_wait_masked are bounded (see
+# include/b200_moe.h): poll device_error() at the step's existing synchronisation point.
+def _on(device, fn, what, *args):
+    with torch.cuda.device(device):
+        L.check(fn(*args, L.stream_of(device)), what)
+
+
+def p2p_copy(dst: torch.Tensor, src: torch.Tensor, device: torch.device):
+    """Copy src (contiguous, a multiple of 16 bytes) into dst with a kernel running on `device`."""
+    n = src.numel() * src.element_size()
+    assert src.is_contiguous() and n % 16 == 0 and dst.numel() * dst.element_size() >= n
+    _on(device, L.lib().b200_p2p_copy, "b200_p2p_copy", L.ptr(dst), L.ptr(src), n)
+
+
+def p2p_copy_row(dst_base: torch.Tensor, row_idx: torch.Tensor, src: torch.Tensor, device: torch.device, seq: torch.Tensor):
+    """dst_base[seq[b], row_idx[b]] = src[b]; dst_base [S, rows, D], src [B, 1, D], row_idx / seq int64 [B]."""
+    B = src.shape[0]
+    row_bytes = src.numel() * src.element_size() // B
+    assert src.is_contiguous() and src.shape[-1] == dst_base.shape[-1] and row_idx.dtype == torch.int64 and seq.dtype == torch.int64
+    _on(device, L.lib().b200_p2p_copy_row, "b200_p2p_copy_row", L.ptr(dst_base), L.ptr(row_idx), L.ptr(src), row_bytes, B,
+        dst_base.stride(0) * dst_base.element_size(), L.ptr(seq))
+
+
 def p2p_sum_rows(dst: torch.Tensor, src: torch.Tensor, device: torch.device, groups: int = 1, dst_stride: int | None = None):
-    """dst[g] = sum of the `rows` rows of group g of src fp32 [groups * rows, n]; dst may live on a peer GPU
-    (dsv41/cukern.py:370-379)."""
+    """dst[g] = sum of the `rows` rows of group g of src fp32 [groups * rows, n]; dst rows `dst_stride` elements apart."""
     total, n = src.shape
-    rows = total // groups
     if dst_stride is None:
         dst_stride = dst.stride(0) if dst.dim() > 1 else n
     assert src.dtype == torch.float32 and dst.dtype == torch.float32 and src.is_contiguous()
-    with torch.cuda.device(device):
-        L.check(L.lib().b200_sum_rows(L.ptr(dst), L.ptr(src), rows, n, groups, int(dst_stride), L.stream_of(device)), "b200_sum_rows")
+    _on(device, L.lib().b200_sum_rows, "b200_sum_rows", L.ptr(dst), L.ptr(src), total // groups, n, groups, int(dst_stride))
+
+
+def p2p_signal(flag_ptrs: torch.Tensor, seq: torch.Tensor, device: torch.device):
+    """Set the int32 flags at the addresses in flag_ptrs (int64 tensor on `device`) to the value of seq (int32 scalar on `device`)."""
+    assert flag_ptrs.dtype == torch.int64 and seq.dtype == torch.int32
+    _on(device, L.lib().b200_p2p_signal, "b200_p2p_signal", L.ptr(flag_ptrs), flag_ptrs.numel(), L.ptr(seq))
+
+
+def p2p_wait(flags: torch.Tensor, seq: torch.Tensor, device: torch.device):
+    """Wait on the stream until all flags (int32 [n] on `device`) >= seq, or until the wait limit runs out (device_error() 3001)."""
+    assert flags.dtype == torch.int32 and seq.dtype == torch.int32
+    _on(device, L.lib().b200_p2p_wait, "b200_p2p_wait", L.ptr(flags), flags.numel(), L.ptr(seq), None)
+
+
+def p2p_wait_masked(flags: torch.Tensor, seq: torch.Tensor, mask: torch.Tensor, device: torch.device):
+    """The same for the flags whose mask entry (int32 [n], computed on the device) is non-zero."""
+    assert flags.dtype == torch.int32 and seq.dtype == torch.int32 and mask.dtype == torch.int32 and mask.numel() == flags.numel()
+    _on(device, L.lib().b200_p2p_wait, "b200_p2p_wait", L.ptr(flags), flags.numel(), L.ptr(seq), L.ptr(mask))
+
+
+def p2p_seq_bump(seq: torch.Tensor, device: torch.device):
+    _on(device, L.lib().b200_p2p_seq_bump, "b200_p2p_seq_bump", L.ptr(seq))
+
+
+_counters: dict = {}
+
+
+def p2p_multicast(dst_ptrs: torch.Tensor, src: torch.Tensor, flag_ptrs: torch.Tensor | None, seq: torch.Tensor, device: torch.device,
+                  counter: torch.Tensor | None = None):
+    """One launch: src into every destination address of dst_ptrs (int64 on `device`), then the flags at flag_ptrs get the value of seq."""
+    n = src.numel() * src.element_size()
+    assert src.is_contiguous() and n % 16 == 0 and dst_ptrs.dtype == torch.int64
+    if flag_ptrs is not None and counter is None:
+        counter = _counters.get(device)
+        if counter is None:
+            counter = _counters[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    _on(device, L.lib().b200_p2p_multicast, "b200_p2p_multicast", L.ptr(dst_ptrs), dst_ptrs.numel(), L.ptr(src), n, L.ptr(flag_ptrs), L.ptr(seq), L.ptr(counter))
+
+
+def p2p_stamp(dst: torch.Tensor, device: torch.device):
+    """The GPU's global nanosecond timer into dst (int64 scalar on `device`), stream-ordered."""
+    _on(device, L.lib().b200_p2p_stamp, "b200_p2p_stamp", L.ptr(dst))
+
+
+def memcpy_async(dst: torch.Tensor, src: torch.Tensor, device: torch.device, nbytes: int | None = None):
+    """Copy-engine transfer on `device`'s current stream; dst may live on another GPU (dsv41/cukern.py:428-434)."""
+    n = src.numel() * src.element_size() if nbytes is None else nbytes
+    _on(device, L.lib().b200_memcpy_async, "b200_memcpy_async", L.ptr(dst), L.ptr(src), int(n))
+
+
+def set_wait_limit_ns(ns: int):
+    """Limit of the messaging waits on the current device (0: the 2 s default)."""
+    L.check(L.lib().b200_set_wait_limit_ns(int(ns)), "b200_set_wait_limit_ns")
+
+
+# --------------------------------------------------------------------------- the expert phase of one token in one call
+_chain_layers: dict = {}
+
+
+def expert_chain(xqp: torch.Tensor, xq: torch.Tensor, eid: torch.Tensor, wt: torch.Tensor, shard: tuple, sh: dict, moe, part: torch.Tensor,
+                 ys: torch.Tensor | None, mode: int | None = None) -> None:
+    """The whole expert phase of ONE token on this GPU (dsv41/cukern.py:504-547): the routed experts of the shard
+    [shard[0], shard[0] + shard[1]) among the token's (eid, wt) pairs -> part fp32 [dim] (routing weights applied) and, when ys is
+    given, the shared expert -> ys bf16 [dim].  xq: the token's FP8 fake-quantised activation bf16 [dim]; xqp (its 8-k permuted copy)
+    and mode belong to the sm_80 kernels and are ignored.  sh: the shard dict {"w13","s13","w2","s2"}; moe: an object with n_experts
+    (or n_routed_experts), inter, swiglu_limit, sh_w13, sh_w2 (W8 containers) as the reference's MoE.  Any dims with dim % 128 == 0 and
+    inter % 128 == 0 (the reference's kernel exists for 5120 / 2304 only).  Runs the 4 launches of the decode path (routing copy +
+    quantisation, gate/up GEMM with SwiGLU, down GEMM, combine)."""
+    from .moe import MoELayer
+    from .w8 import W8
+    dev = L.require_cuda(xq, eid, wt, part, ys)
+    key = (id(sh), id(moe), shard[0], ys is not None)
+    layer = _chain_layers.get(key)
+    if layer is None:
+        def as_w8(w):
+            return w if isinstance(w, W8) else W8(w.w8, w.s8, permuted=True)
+        n_exp = getattr(moe, "n_experts", None) or getattr(moe, "n_routed_experts", None) or (shard[0] + shard[1])
+        layer = _chain_layers[key] = MoELayer(sh["w13"], sh["s13"], sh["w2"], sh["s2"], n_experts=int(n_exp), topk=eid.numel(),
+                                              sh_w13=as_w8(moe.sh_w13) if ys is not None else None, sh_w2=as_w8(moe.sh_w2) if ys is not None else None,
+                                              swiglu_limit=float(moe.swiglu_limit), shard_start=int(shard[0]))
+    x = xq.reshape(1, -1)
+    assert x.shape[1] == layer.dim and part.dtype == torch.float32 and part.numel() == layer.dim and part.is_contiguous()
+    layer.forward(x, None, eid=eid.reshape(1, -1), wt=wt.reshape(1, -1), final=False, want_routed=True, routed_out=part.view(1, -1), want_shared=ys is not None,
+                  shared_out=ys.view(1, -1) if ys is not None else None)
 
 
 # --------------------------------------------------------------------------- block-scaled tensor-core path (FP8 activations)

@@ -113,18 +113,25 @@ class MoELayer:
         return linear_w(hs, self.sh_w2)
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None, *, xf: torch.Tensor | None = None, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
-                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, want_shared: bool = False, prof_events=None):
+                x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, want_shared: bool = False, prof_events=None,
+                eid: torch.Tensor | None = None, wt: torch.Tensor | None = None, shared_out: torch.Tensor | None = None, routed_out: torch.Tensor | None = None):
         """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E]; logits=None (the layer was
         built with gate_w): the router projection xf @ gate_w^T runs inside the call, xf fp32 [T, D] or None for x.float()
         (dsv41/decode.py:449, dsv41/model.py:1615).
+        eid int32 / wt fp32 [T, topk]: routing decided by the caller instead of logits (at most 64 tokens, E8M0 formats).
         Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
-        and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel."""
+        and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel.  shared_out / routed_out:
+        caller-provided buffers for the shared expert's result (bf16) and the routed sum (fp32) instead of fresh ones."""
         dev = L.require_cuda(x, logits, out)
         # rows may be strided (views into a wider buffer), the elements of a row are contiguous
         assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.stride(1) == 1
         assert (x.stride(0) * 2) % 16 == 0 and x.data_ptr() % 16 == 0
         T = x.shape[0]
-        if logits is None:
+        given = eid is not None
+        if given:
+            assert wt is not None and eid.dtype == torch.int32 and wt.dtype == torch.float32 and eid.is_contiguous() and wt.is_contiguous()
+            assert eid.numel() == T * self.topk and wt.numel() == T * self.topk and T <= 64 and self._atoms is not None
+        elif logits is None:
             assert self.gate_w is not None, "forward() without logits needs the layer's gate_w"
             assert xf is None or (xf.shape == (T, self.dim) and xf.dtype == torch.float32 and xf.stride(1) == 1 and xf.is_cuda)
         else:
@@ -133,11 +140,11 @@ class MoELayer:
         mx = self._use_mx(T)
         if final and out is None:
             out = torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16)
-        routed = torch.empty(T, self.dim, device=dev, dtype=torch.float32) if want_routed else None
-        eid = torch.empty(T, self.topk, device=dev, dtype=torch.int32) if want_route else None
-        wt = torch.empty(T, self.topk, device=dev, dtype=torch.float32) if want_route else None
+        routed = (routed_out if routed_out is not None else torch.empty(T, self.dim, device=dev, dtype=torch.float32)) if want_routed else None
+        eid_o = torch.empty(T, self.topk, device=dev, dtype=torch.int32) if want_route else None
+        wt_o = torch.empty(T, self.topk, device=dev, dtype=torch.float32) if want_route else None
         shared = with_shared and self.sh_w13 is not None and (final or want_shared)
-        ys = torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16) if (want_shared and shared) else None
+        ys = (shared_out if shared_out is not None else torch.empty(T, self.dim, device=dev, dtype=torch.bfloat16)) if (want_shared and shared) else None
         # the argument block is kept per (token count, engine): a decode loop calls this tens of thousands of times per second, so
         # everything that does not change from call to call (weights, formats, router settings, workspace) is filled in once
         key = (T, mx)
@@ -177,8 +184,9 @@ class MoELayer:
         a.out = out.data_ptr() if final else None
         a.routed_out = routed.data_ptr() if routed is not None else None
         a.shared_out = ys.data_ptr() if ys is not None else None
-        a.eid_out = eid.data_ptr() if eid is not None else None
-        a.wt_out = wt.data_ptr() if wt is not None else None
+        a.eid_out = eid_o.data_ptr() if eid_o is not None else None
+        a.wt_out = wt_o.data_ptr() if wt_o is not None else None
+        a.eid_in, a.wt_in = (eid.data_ptr(), wt.data_ptr()) if given else (None, None)
         if prof_events is not None:  # (start, stop) torch.cuda.Event pair, already created (recorded once), timing enabled
             a.prof_start, a.prof_stop = prof_events[0].cuda_event, prof_events[1].cuda_event
         else:
@@ -189,7 +197,7 @@ class MoELayer:
         if want_routed:
             res.append(routed)
         if want_route:
-            res += [eid, wt]
+            res += [eid_o, wt_o]
         if want_shared:
             res.append(ys)
         return res[0] if len(res) == 1 else tuple(res)

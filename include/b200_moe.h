@@ -117,6 +117,21 @@ int b200_fp4_grouped_gemm_static(const void* x, long long x_ld, int x_perm8, con
                                  int n_groups, const int* pair_tok, const int* pair_out, const float* pair_w, int n_pairs, int shard_start, int shard_n,
                                  int zero_out, int accumulate, float* out, long long out_ld, cudaStream_t stream);
 
+/* ---- bucketing of (row, expert) pairs for the grouped GEMMs.  Replaces GroupedPairs (dsv41/moe_kernels.py:76-132: stable argsort by
+ * expert, tile table of at most block_m pairs per tile) and GroupedPairs.make_p2 (dsv41/moe_kernels.py:134-158).
+ *   expert int32 [n_pairs] (ids outside [0, n_experts) are dropped); row_in / row_out int32 [n_pairs] or NULL (= pair index); weight fp32
+ *   [n_pairs] or NULL (= 1).  Outputs, all int32 / fp32 [n_pairs]: order (sorted position -> original pair, stable), s_expert, s_row_in,
+ *   s_row_out, s_weight (the inputs in sorted order); tile_expert / tile_start / tile_count int32 [b200_group_pairs_max_tiles(...)] (tiles in
+ *   expert order; unused entries: expert -1, count 0); n_tiles int32 [1].  n_experts <= 1024.  No host synchronisation.
+ * b200_regroup_pairs gathers new rows / weights into an existing order: s_x[i] = x[order[i]]. */
+int b200_group_pairs_max_tiles(int n_pairs, int n_experts, int block_m);
+size_t b200_group_pairs_workspace_bytes(int n_experts);
+int b200_group_pairs(const int* expert, const int* row_in, const int* row_out, const float* weight, int n_pairs, int n_experts, int block_m, int* order,
+                     int* s_expert, int* s_row_in, int* s_row_out, float* s_weight, int* tile_expert, int* tile_start, int* tile_count, int* n_tiles,
+                     void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int b200_regroup_pairs(const int* order, int n_pairs, const int* row_in, const int* row_out, const float* weight, int* s_row_in, int* s_row_out,
+                       float* s_weight, cudaStream_t stream);
+
 /* ---- block-scaled FP8 dense GEMV / small-M GEMM.  Replaces fp8_gemv (dsv41/cukern.py:80-96), fp8_gemv_m1
  * (dsv41/cukern.py:116-133) and fp8_gemm_tc (dsv41/cukern.py:165-221, group_cols = 0).
  *   out[m, :] = x[m, :] @ dequant(w8, s)^T;  x bf16 [M, K] (row stride x_ld); w8 e4m3 [N, K];
@@ -184,6 +199,10 @@ typedef struct b200_moe_args {
      * With all of them given (and E8M0 formats), batches of up to 64 tokens run on the weight-stream kernels: 4 launches per call, the
      * k range of every launch cut evenly over the SMs.  NULL: the kernels that read the scales in checkpoint order are used. */
     const void *s13_atoms, *s2_atoms, *sh_s13_atoms, *sh_s2_atoms;
+    /* optional: routing decided by the caller, int32 / fp32 [tokens, topk] (the argument form of cukern.expert_chain,
+     * dsv41/cukern.py:504-547): no router runs and `logits` may be NULL.  Needs the scale atoms above and at most 64 tokens. */
+    const int* eid_in;
+    const float* wt_in;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);
@@ -235,6 +254,27 @@ int b200_hc_pre_norm_quant2(const void* x, const float* pre, const void* w, int 
                             float* yf, void* yqp, cudaStream_t stream);
 int b200_hc_post2(const void* x, const float* y2, const void* ys, long long y2_row_stride, long long y2_sum_stride, int nsum, void* residual,
                   const float* post, const float* comb, int rows, int hc, int dim, cudaStream_t stream);
+
+/* ---- device-side messaging between GPUs for the expert-parallel decode protocol.  Replace the kernels of dsv41/cuda/p2p.cu behind
+ * dsv41/cukern.py:348-434 (p2p_copy, p2p_copy_row, p2p_signal, p2p_wait, p2p_wait_masked, p2p_seq_bump, p2p_multicast, p2p_stamp) and
+ * memcpy_async.  Destinations and flags may be local memory or any memory of another GPU that the calling context can address; fan-out is
+ * a loop of ordinary stores (no multicast objects).  Sizes are multiples of 16 bytes, pointers 16-byte aligned.
+ *   flag_ptrs / dst_ptrs: DEVICE arrays of addresses; seq: device int32 holding the step number that signal publishes and wait expects
+ *   (flags count upwards, a wait is satisfied by flag >= *seq); mask: device int32 [n] or NULL, zero entries are not waited for;
+ *   counter: device uint32, zero before the first use, resets itself.
+ * b200_p2p_wait is BOUNDED, unlike the reference's: after the limit (2 s; b200_set_wait_limit_ns changes it, 0 restores the default) it
+ * stores 3001 (3002 with a mask) in the device error word and returns, leaving the stream usable. */
+int b200_p2p_copy(void* dst, const void* src, long long nbytes, cudaStream_t stream);
+int b200_p2p_copy_row(void* dst_base, const long long* row_idx, const void* src, long long row_bytes, int n_rows, long long batch_stride_bytes,
+                      const long long* seq, cudaStream_t stream);
+int b200_p2p_signal(int* const* flag_ptrs, int n, const int* seq, cudaStream_t stream);
+int b200_p2p_wait(const int* flags, int n, const int* seq, const int* mask, cudaStream_t stream);
+int b200_p2p_seq_bump(int* seq, cudaStream_t stream);
+int b200_p2p_multicast(void* const* dst_ptrs, int n_dst, const void* src, long long nbytes, int* const* flag_ptrs, const int* seq, unsigned int* counter,
+                       cudaStream_t stream);
+int b200_p2p_stamp(long long* dst, cudaStream_t stream);
+int b200_memcpy_async(void* dst, const void* src, long long nbytes, cudaStream_t stream);
+int b200_set_wait_limit_ns(unsigned long long ns);
 
 /* ---- device error word.  Every device-side wait of this library is bounded; one that runs out of time stores a non-zero
  * code instead of hanging.  Synchronises `stream`, returns the code in *code (0 = none) and clears it. */

@@ -230,3 +230,32 @@ def test_layer_starts_from_hidden_state(mods, dev, T, use_xf):
     again = layer.forward(x.to(dev), None, xf=xf.to(dev) if use_xf else None)
     assert torch.equal(again, got)  # the k-split sums are added in a fixed order: same logits, same routing, same output
     assert mods.cukern.device_error(dev) == 0
+
+
+@pytest.mark.parametrize("with_shared", [True, False])
+def test_expert_chain_entry_point(mods, oracle, dev, with_shared):
+    """cukern.expert_chain with the reference's argument list (dsv41/cukern.py:504-547): one token, routing given as (eid, wt), one
+    shard of the experts -> routed partial sum fp32 [dim] and the shared expert's result bf16 [dim]."""
+    from types import SimpleNamespace
+    E, D, I, topk, start, n = 16, 512, 256, 4, 4, 8
+    ex = mods.synth.make_experts(E, D, I, seed=71, scale_lo=116, scale_hi=122)
+    shd = mods.synth.make_shared(D, I, seed=72, kind="e8m0")
+    x = mods.synth.make_tokens(1, D, 73)
+    logits = mods.synth.make_logits(1, E, 74, topk=topk)
+    eid, wt = oracle.gate_topk(logits.float(), None, 1.0, topk, 1.0, "softmax", True)
+    xq = oracle.fake_quant_fp8(x, 32)
+    sh = {"device": dev, "start": start, "n": n, **{k: ex[k][start:start + n].to(dev) for k in ("w13", "s13", "w2", "s2")}}
+    moe = SimpleNamespace(n_experts=E, inter=I, swiglu_limit=10.0, sh_w13=mods.w8.W8(shd["w13"].to(dev), shd["s13"].to(dev)),
+                          sh_w2=mods.w8.W8(shd["w2"].to(dev), shd["s2"].to(dev)))
+    part = torch.full((D,), float("nan"), device=dev)
+    ys = torch.empty(D, device=dev, dtype=torch.bfloat16) if with_shared else None
+    xqd = xq[0].to(dev)
+    for _ in range(2):  # the second call reuses the cached layer
+        mods.cukern.expert_chain(mods.cukern.permute_x(xqd.view(1, -1))[0], xqd, eid[0].to(dev), wt[0].to(dev), (start, n), sh, moe, part, ys)
+    assert mods.cukern.device_error(dev) == 0
+    fetch = lambda ids: tuple(ex[k][ids] for k in ("w13", "s13", "w2", "s2"))
+    ref = oracle.moe_rows(x, eid, wt, fetch, None, 10.0, shard=(start, n))
+    assert rel_err(part.view(1, -1), ref["routed"]) <= 2e-3
+    if with_shared:
+        want = oracle.shared_expert(xq, shd["w13"], shd["s13"], shd["w2"], shd["s2"], 10.0)
+        assert rel_err(ys.view(1, -1), want) <= 1e-2

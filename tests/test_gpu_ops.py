@@ -133,7 +133,7 @@ def test_fp4_gemm_tc_groups_and_shards(mods, oracle, dev, G, M):
     """Grouped form of dsv41/test_fp4_tc.py:31-41 plus the shard rule: foreign groups are skipped, zero_out zeroes their rows."""
     E, N, K = 8, 256, 1024
     w, s, g = _experts(E, N, K, 100 + G * 10 + M, 112, 128)
-    x = mods.quant.fake_quant_fp8((torch.randn(M, K, generator=g) * 2).to(torch.bfloat16), 32)
+    x = oracle.fake_quant_fp8((torch.randn(M, K, generator=g) * 2).to(torch.bfloat16), 32)
     xp = mods.cukern.permute_x(x.to(dev))
     experts = torch.arange(G, dtype=torch.int32)
     grp_start = torch.arange(0, G * M + 1, M, dtype=torch.int32)
@@ -156,13 +156,48 @@ def test_fp4_gemm_tc_groups_and_shards(mods, oracle, dev, G, M):
         assert (y.cpu()[~mask] == 7.0).all()
 
 
+def test_grouped_pairs_matches_oracle_grouping(mods, oracle, dev):
+    """The device bucketing against the checker's stable grouping: same order, same tiles (in expert order, at most block_m pairs each;
+    the unused capacity of the tables carries expert -1 / count 0), ids outside the expert range dropped, make_p2 keeps the buckets."""
+    g = torch.Generator().manual_seed(0)
+    for n_pairs, E, bm in ((10, 16, 16), (400, 16, 64), (1000, 384, 64), (24576, 384, 64)):
+        eid = torch.randint(0, E, (n_pairs,), generator=g)
+        row = torch.randint(0, 1000, (n_pairs,), generator=g)
+        wt = torch.rand(n_pairs, generator=g)
+        gp = mods.moe_kernels.GroupedPairs(eid.to(dev), row.to(dev), row.clone().to(dev), wt.to(dev), bm, n_experts=E)
+        assert gp.n_pairs == n_pairs and gp.block_m == bm
+        order, counts = oracle.group_pairs(eid, E)
+        assert torch.equal(gp.order.cpu(), order)
+        assert torch.equal(gp.expert.cpu(), eid[order.long()].int())
+        assert torch.equal(gp.row_in.cpu(), row[order.long()].int()) and torch.equal(gp.weight.cpu(), wt[order.long()])
+        exp_tiles, start = [], 0
+        for e in range(E):
+            c = int(counts[e])
+            for t0 in range(0, c, bm):
+                exp_tiles.append((e, start + t0, min(bm, c - t0)))
+            start += c
+        n = int(gp.n_tiles.item())
+        got = list(zip(gp.tile_expert.tolist(), gp.tile_start.tolist(), gp.tile_count.tolist()))
+        assert n == len(exp_tiles) and got[:n] == exp_tiles
+        assert all(t == (-1, 0, 0) for t in got[n:])
+        row2 = torch.randint(0, 50, (n_pairs,), generator=g)
+        p2 = gp.make_p2(row2.to(dev), row.to(dev), None)
+        assert torch.equal(p2.row_in.cpu(), row2[order.long()].int()) and p2.tile_start is gp.tile_start and p2.weight is gp.weight
+        w2 = torch.rand(n_pairs, generator=g)
+        assert torch.equal(gp.make_p2(row.to(dev), row.to(dev), w2.to(dev)).weight.cpu(), w2[order.long()])
+    # ids outside [0, E) are dropped
+    eid = torch.tensor([3, -1, 2, 3, 99, 0])
+    gp = mods.moe_kernels.GroupedPairs(eid.to(dev), torch.arange(6).to(dev), torch.arange(6).to(dev), torch.ones(6).to(dev), 4, n_experts=8)
+    assert gp.order.cpu().tolist()[:4] == [5, 2, 0, 3] and int(gp.tile_count.sum()) == 4
+
+
 def test_grouped_fp4_shard_zero_out_with_permuted_output_rows(mods, oracle, dev):
     """zero_out clears the rows the foreign pairs WRITE (pair_out), not the rows at their positions, and never a row beyond the
     output: output rows = tokens here (fewer than pairs), several pairs of a token would share a row, so each pair gets its own
     slot of a [T * topk] buffer addressed through pair_out."""
     E, N, K, T, topk = 8, 256, 512, 5, 3
     w, s, g = _experts(E, N, K, 321, 112, 128)
-    x = mods.quant.fake_quant_fp8((torch.randn(T, K, generator=g) * 2).to(torch.bfloat16), 32)
+    x = oracle.fake_quant_fp8((torch.randn(T, K, generator=g) * 2).to(torch.bfloat16), 32)
     eid = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)])
     order = torch.argsort(eid.flatten(), stable=True)
     experts, counts = torch.unique(eid.flatten()[order], return_counts=True)
@@ -209,7 +244,7 @@ def _rand_fp8(N, K, g, lo=110, hi=130):
 def test_fp8_gemm_e8m0(mods, oracle, dev, M, N, K):
     g = torch.Generator().manual_seed(N + K + M)
     w, s = _rand_fp8(N, K, g)
-    x = mods.quant.fake_quant_fp8((torch.randn(M, K, generator=g) * 2).to(torch.bfloat16), 32)
+    x = oracle.fake_quant_fp8((torch.randn(M, K, generator=g) * 2).to(torch.bfloat16), 32)
     ref = oracle.fp8_gemm(x, w, s)
     y = mods.cukern.fp8_gemm_tc(x.to(dev), mods.w8.permute_k(w).to(dev), s.to(dev), out_dtype=torch.float32)
     assert rel_err(y, ref) < 2e-3

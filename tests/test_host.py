@@ -47,34 +47,6 @@ def test_operators_refuse_cpu_tensors(mods):
         mods.fused2.gate_topk(torch.zeros(1, 8), None, 1.0, 2, 1.0, "softmax", True)
 
 
-def test_grouped_pairs_matches_oracle_grouping(mods, oracle):
-    g = torch.Generator().manual_seed(0)
-    for n_pairs, E, bm in ((10, 16, 16), (400, 16, 64), (1000, 384, 64)):
-        eid = torch.randint(0, E, (n_pairs,), generator=g)
-        row = torch.arange(n_pairs)
-        wt = torch.rand(n_pairs, generator=g)
-        gp = mods.moe_kernels.GroupedPairs(eid, row, row.clone(), wt, bm, n_experts=E)
-        assert gp.n_pairs == n_pairs and gp.block_m == bm
-        if n_pairs <= 64:
-            assert torch.equal(gp.tile_expert, eid.int()) and torch.equal(gp.tile_count, torch.ones(n_pairs, dtype=torch.int32))
-            continue
-        order, counts = oracle.group_pairs(eid, E)
-        assert torch.equal(gp.order.int(), order)
-        assert torch.equal(gp.expert, eid[order.long()].int())
-        # tiles: every expert's pairs cut into blocks of block_m, in expert order
-        exp_tiles = []
-        start = 0
-        for e in range(E):
-            c = int(counts[e])
-            for t0 in range(0, c, bm):
-                exp_tiles.append((e, start + t0, min(bm, c - t0)))
-            start += c
-        got = list(zip(gp.tile_expert.tolist(), gp.tile_start.tolist(), gp.tile_count.tolist()))
-        assert got == exp_tiles
-        p2 = gp.make_p2(row, row, None)
-        assert torch.equal(p2.row_in, gp.row_in) and p2.tile_start is gp.tile_start and p2.weight is gp.weight
-
-
 def test_shard_ranges_and_token_split(mods):
     assert mods.ep.shard_ranges(384, 8) == [(48 * r, 48) for r in range(8)]
     assert mods.ep.shard_ranges(384, 2) == [(0, 192), (192, 192)]
@@ -94,10 +66,21 @@ def test_w8_permutation_and_dequant(mods):
     assert both.shape == (128, 128) and both.s8.shape == (4, 4)
 
 
-def test_quant_module_matches_oracle_on_cpu(mods, oracle):
+def test_quant_formats_and_torch_statement_of_the_activation_quantisation(mods, oracle):
+    from oracle import torch_spec
     x = (torch.randn(3, 128) * 3).to(torch.bfloat16)
-    assert torch.equal(mods.quant.fake_quant_fp8(x, 32).view(torch.int16), oracle.fake_quant_fp8(x, 32).view(torch.int16))
-    assert mods.quant.round_e2m1(torch.tensor([0.75, 1.25, 2.5, 5.0])).tolist() == [1.0, 1.0, 2.0, 4.0]
+    assert torch.equal(torch_spec.fake_quant_fp8(x, 32).view(torch.int16), oracle.fake_quant_fp8(x, 32).view(torch.int16))
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        mods.quant.fake_quant_fp8(x, 32)  # the package has no CPU path
+    assert mods.quant.round_e2m1(torch.tensor([0.75, 1.25, 2.5, 5.0, -0.25, 7.0, 0.2])).tolist() == [1.0, 1.0, 2.0, 4.0, -0.0, 6.0, 0.0]
+    assert mods.quant.e8m0_to_float(torch.tensor([127, 123, 130, 1], dtype=torch.uint8)).tolist() == [1.0, 0.0625, 8.0, 2.0 ** -126]
+    packed = torch.tensor([[0x21, 0xF8]], dtype=torch.uint8)
+    assert mods.quant.unpack_fp4(packed).tolist() == [[0.5, 1.0, -0.0, -6.0]]
+    g = torch.Generator().manual_seed(1)
+    w = torch.randint(0, 256, (4, 32), dtype=torch.uint8, generator=g)
+    s = torch.randint(120, 130, (4, 2), dtype=torch.uint8, generator=g)
+    ref = oracle.fp4_gemm(torch.eye(64).to(torch.bfloat16), w, s).T  # rows of the dequantised matrix through the checker
+    assert torch.equal(mods.quant.dequant_fp4(w, s).float(), ref)
 
 
 def test_synthetic_generators(mods):
