@@ -338,6 +338,20 @@ def bench_fp8_gemv(g, dev, steps: int, warmup: int, peak: float):
             "frac_min": min(fr), "frac_max": max(fr), "frac_mean": statistics.mean(fr), "shapes": res}
 
 
+def finish_ranks(graphs=None):
+    """End of a multi-rank run: every rank has finished its work (barrier + synchronize), the captured graphs are released first, and
+    the process leaves without tearing the communicator down (a teardown with NCCL work captured in live graphs can block for minutes)."""
+    import torch.distributed as dist
+    if graphs:
+        graphs.clear()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def run_gpu(args):
     import __graft_entry__ as g
     rank, local_rank, world = dist_env()
@@ -425,12 +439,45 @@ def run_gpu(args):
     NP = pool_size(S)
     uniq = [int(torch.unique(l.float().topk(TOPK, dim=-1).indices).numel()) for l in ls_h]
 
+    # Expert-parallel decode steps are replayed from CUDA graphs (one per input buffer): a step is a dozen small launches and two
+    # collectives, and a serving loop would not pay their host-side launch cost every step either.  Every rank captures the same sequence.
+    graphs = {}
+
+    def graph_for(key, xin, lin, outbuf):
+        if world == 1 or S > 64 or args.no_graph:
+            return None
+        if key not in graphs:
+            try:
+                side = torch.cuda.Stream(dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        epl.forward(xin, lin, counts, out=outbuf)
+                torch.cuda.current_stream(dev).wait_stream(side)
+                torch.cuda.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    epl.forward(xin, lin, counts, out=outbuf)
+                graphs[key] = gr
+            except Exception as e:  # capture refused: run the step eagerly and say so
+                graphs[key] = None
+                graphs["error"] = f"{type(e).__name__}: {e}"[:200]
+        return graphs[key]
+
+    x_static, l_static = torch.empty_like(xs[0]), torch.empty_like(ls[0])
+
     def step_resident(i):
         j = i % NP
         if world == 1:
             layer.forward(xs[j], ls[j], out=out)
+            return
+        gr = graph_for("resident", x_static, l_static, out)
+        if gr is None:
+            epl.forward(xs[j], ls[j], counts, out=out)
         else:
-            out.copy_(epl.forward(xs[j], ls[j], counts))
+            x_static.copy_(xs[j])
+            l_static.copy_(ls[j])
+            gr.replay()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -473,7 +520,11 @@ def run_gpu(args):
         if world == 1:
             layer.forward(xd[b], ld[b], out=outs[b])
         else:
-            outs[b].copy_(epl.forward(xd[b], ld[b], counts))
+            gr = graph_for(("e2e", b), xd[b], ld[b], outs[b])
+            if gr is None:
+                epl.forward(xd[b], ld[b], counts, out=outs[b])
+            else:
+                gr.replay()
         ev_cmp[b].record(cur)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_cmp[b])
@@ -516,13 +567,17 @@ def run_gpu(args):
             fp = sum(cp[:rank])
             xp = [synth.make_tokens(Tp, D, SEED + 40 + i)[fp:fp + cp[rank]].to(dev) for i in range(2)]
             lp = [synth.make_logits(Tp, E, SEED + 3, topk=TOPK, rotate=ROTATE * i)[fp:fp + cp[rank]].to(dev) for i in range(2)]
-            msp = max_over_ranks(time_steps(lambda i: epl.forward(xp[i & 1], lp[i & 1], cp), 5, 3, barrier))
+            op = torch.empty(cp[rank], D, device=dev, dtype=torch.bfloat16)
+            msp = max_over_ranks(time_steps(lambda i: epl.forward(xp[i & 1], lp[i & 1], cp, out=op), 5, 3, barrier))
             fl = Tp * TOPK * (2.0 * D * 2 * I + 2.0 * I * D)
             pre = {"tokens": Tp, "ms_per_step": msp, "tokens_per_s": Tp / (msp * 1e-3), "routed_tflops_all_gpus": fl / (msp * 1e-3) / 1e12,
                    "frac_of_bf16_burst_per_gpu": fl / (msp * 1e-3) / 1e12 / world / tpeak}
             del xp, lp
         if rank == 0:
             gbs = max_rank_bytes / (ms * 1e-3) / 1e9
+            line["config"]["cuda_graph"] = bool(graphs.get("resident")) if S <= 64 else False
+            if "error" in graphs:
+                line["config"]["cuda_graph_error"] = graphs["error"]
             line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_source": peak_src,
                                 "what": "whole step of the rank that streams most: (its distinct local experts x 13,369,344 B + its share of the shared expert) / max-over-ranks step time",
                                 "max_rank_bytes_per_step": max_rank_bytes, "phases_ms": phases}
@@ -531,7 +586,7 @@ def run_gpu(args):
             code = cukern.device_error(dev)
             line["device_error"] = code
             print(json.dumps(line), flush=True)
-        dist.destroy_process_group()
+        finish_ranks(graphs)
         return
 
     # ---- single GPU: kernel-level roofline from a separate short pass with events around the dominant kernel
@@ -614,6 +669,7 @@ def main():
     ap.add_argument("--workload", default="decode64", choices=sorted(WORKLOADS) + ["fp8_gemv"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="expert-parallel decode: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--engine", type=int, default=0, choices=[0, 1, 2], help="0 automatic, 1 weight-streaming kernels, 2 tcgen05 block-scaled kernels")

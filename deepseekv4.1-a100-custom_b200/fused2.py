@@ -28,13 +28,15 @@ def gate_topk(scores: torch.Tensor, bias: torch.Tensor | None, temp: float, topk
     return eid, wt
 
 
-def moe_combine(y2: torch.Tensor, ys: torch.Tensor | None) -> torch.Tensor:
+def moe_combine(y2: torch.Tensor, ys: torch.Tensor | None, out: torch.Tensor | None = None) -> torch.Tensor:
     """The MoE branch of hc_post2_ (dsv41/fused2.py:518-523): bf16( sum over dim 1 of y2 fp32 [B, nsum, d] + ys bf16 [B, d] )."""
-    dev = L.require_cuda(y2, ys)
+    dev = L.require_cuda(y2, ys, out)
     B, nsum, d = y2.shape
     y2c = y2.to(torch.float32).contiguous()
     ysc = ys.to(torch.bfloat16).contiguous() if ys is not None else None
-    out = torch.empty(B, d, device=dev, dtype=torch.bfloat16)
+    if out is None:
+        out = torch.empty(B, d, device=dev, dtype=torch.bfloat16)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (B, d)
     with torch.cuda.device(dev):
         L.check(L.lib().b200_moe_combine(L.ptr(y2c), L.ptr(ysc), L.ptr(out), B, nsum, d, L.stream_of(dev)), "b200_moe_combine")
     return out

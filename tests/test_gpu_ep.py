@@ -52,4 +52,4 @@ def test_expert_parallel_two_gpus_matches_one(tmp_path, T_total):
     mp.spawn(_rank_main, args=(2, 29600 + T_total % 50, T_total, out), nprocs=2, join=True)
     for r in range(2):
         res = torch.load(f"{out}.{r}")
-        assert res["rows"] > 0 and res["err"] < 2e-2  # bf16 rounding of a differently ordered fp32 sum
+        assert res["rows"] > 0 and res["err"] <= 1e-2  # bf16 rounding of a differently ordered fp32 sum

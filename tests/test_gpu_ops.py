@@ -299,3 +299,55 @@ def test_p2p_sum_rows(mods, dev):
     dst = torch.zeros(3, 512, device=dev)
     mods.cukern.p2p_sum_rows(dst, src, dev, groups=3)
     assert torch.allclose(dst[:, :500], src.view(3, 6, 500).sum(1), atol=1e-5)
+
+
+@pytest.mark.parametrize("dual", [True, False])
+def test_scale_atoms_are_a_pure_relayout(mods, dev, dual):
+    """The load-time re-layout of the scales (b200_scale_atoms): every byte of the result is the byte of the checkpoint-order tensor that the
+    documented layout names; rows past the matrix read as 127 (scale 1)."""
+    g = torch.Generator().manual_seed(9)
+    E, K = 3, 512
+    N = 2 * 160 if dual else 400     # inter = 160: the second tile of a gate | up matrix is ragged; 400 rows: the second 256-row tile is ragged
+    s = torch.randint(1, 255, (E, N, K // 32), dtype=torch.uint8, generator=g)
+    atoms = mods.cukern.scale_atoms(s.to(dev), N, K, dual).cpu()      # [E, tiles, K/128, 2, 512]
+    tiles = atoms.shape[1]
+    assert tiles == 2 and atoms.shape[2] == K // 128
+    inter = N // 2
+    for e in range(E):
+        for t in range(tiles):
+            for rb in range(2):
+                for r in (0, 31, 32, 77, 127):
+                    row, ok = ((rb * inter + t * 128 + r), t * 128 + r < inter) if dual else ((t * 256 + rb * 128 + r), t * 256 + rb * 128 + r < N)
+                    for kb in range(K // 128):
+                        got = atoms[e, t, kb, rb, (r % 32) * 16 + (r // 32) * 4:(r % 32) * 16 + (r // 32) * 4 + 4]
+                        want = s[e, row, kb * 4:kb * 4 + 4] if ok else torch.full((4,), 127, dtype=torch.uint8)
+                        assert torch.equal(got, want), (e, t, rb, r, kb)
+    # the dense FP8 format (one scale per 32 rows x 32 k) expands every scale row to its 32 weight rows
+    s8 = torch.randint(1, 255, ((N + 31) // 32, K // 32), dtype=torch.uint8, generator=g)
+    a8 = mods.cukern.scale_atoms(s8.to(dev), N, K, dual).cpu()
+    r = 45
+    row = r if not dual else r
+    assert torch.equal(a8[0, 0, 1, 0, (r % 32) * 16 + (r // 32) * 4:(r % 32) * 16 + (r // 32) * 4 + 4], s8[row // 32, 4:8])
+
+
+def test_loader_relayout_and_layer_from_shard(mods, oracle, dev):
+    """Loader end to end on the device: checkpoint-style tensors -> shard dict -> scale atoms -> layer; the layer's output matches the
+    checker on the same weights."""
+    import importlib
+    load = importlib.import_module("dsv41_b200.load")
+    E, D, I, topk, T = 8, 512, 256, 2, 5
+    ex = mods.synth.make_experts(E, D, I, seed=5, scale_lo=116, scale_hi=122)
+    ck = {}
+    for e in range(E):
+        q = f"layers.0.ffn.experts.{e}."
+        ck[q + "w1.weight"], ck[q + "w3.weight"] = ex["w13"][e, :I], ex["w13"][e, I:]
+        ck[q + "w1.scale"], ck[q + "w3.scale"] = ex["s13"][e, :I], ex["s13"][e, I:]
+        ck[q + "w2.weight"], ck[q + "w2.scale"] = ex["w2"][e], ex["s2"][e]
+    shard = load.relayout_scales(load.stack_experts(ck, "layers.0.", 2, 4, dev))
+    assert torch.equal(shard["w13"].cpu(), ex["w13"][2:6]) and shard["s13_atoms"].shape[:3] == (4, I // 128, D // 128)
+    layer = load.layer_from_shard(shard, E, topk=topk, swiglu_limit=10.0)
+    x = mods.synth.make_tokens(T, D, 6)
+    logits = mods.synth.make_logits(T, E, 7, topk=topk)
+    routed = layer.forward(x.to(dev), logits.to(dev), final=False, want_routed=True)
+    ref = oracle.moe_layer(x, logits.float(), None, ex["w13"][2:6], ex["s13"][2:6], ex["w2"][2:6], ex["s2"][2:6], None, topk=topk, shard=(2, 4), n_experts=E)
+    assert rel_err(routed, ref["routed"]) <= 2e-3

@@ -50,8 +50,43 @@ def test_operators_refuse_cpu_tensors(mods):
 def test_shard_ranges_and_token_split(mods):
     assert mods.ep.shard_ranges(384, 8) == [(48 * r, 48) for r in range(8)]
     assert mods.ep.shard_ranges(384, 2) == [(0, 192), (192, 192)]
-    assert mods.ep.shard_ranges(10, 4) == [(0, 3), (3, 3), (6, 2), (8, 2)]
+    assert mods.ep.shard_ranges(10, 4) == [(0, 2), (2, 3), (5, 2), (7, 3)]  # boundaries at floor(10 r / 4), as dsv41/load.py:304-305
+    assert mods.ep.split_tokens(10, 4) == [(0, 3), (3, 3), (6, 2), (8, 2)]
     assert sum(n for _, n in mods.ep.split_tokens(64, 3)) == 64
+
+
+def test_loader_stacks_experts_and_shards(pkg):
+    """Per-expert checkpoint tensors -> stacked tensors and shard dicts, bit for bit as the reference's loader lays them out
+    (dsv41/load.py:213-249): w13 = [w1; w3] along the rows, shards hold contiguous global expert ranges."""
+    import importlib
+    load = importlib.import_module("dsv41_b200.load")
+    g = torch.Generator().manual_seed(3)
+    E, inter, dim, p = 6, 64, 128, "layers.3."
+    ck = {}
+    for e in range(E):
+        q = f"{p}ffn.experts.{e}."
+        for part, (n, k) in (("w1", (inter, dim)), ("w3", (inter, dim)), ("w2", (dim, inter))):
+            ck[q + part + ".weight"] = torch.randint(-128, 128, (n, k // 2), dtype=torch.int8, generator=g)   # any 1-byte dtype
+            ck[q + part + ".scale"] = torch.randint(100, 140, (n, k // 32), dtype=torch.uint8, generator=g)
+    ck[p + "ffn.gate.weight"] = torch.zeros(E, dim)
+    assert load.expert_ids(ck.keys(), p) == list(range(E))
+    full = load.load_experts(ck, p, "cpu")
+    assert full["experts.w13"].shape == (E, 2 * inter, dim // 2) and full["experts.s2"].shape == (E, dim, inter // 32)
+    for e in (0, 5):
+        q = f"{p}ffn.experts.{e}."
+        assert torch.equal(full["experts.w13"][e, :inter], ck[q + "w1.weight"].view(torch.uint8))
+        assert torch.equal(full["experts.w13"][e, inter:], ck[q + "w3.weight"].view(torch.uint8))
+        assert torch.equal(full["experts.s13"][e, inter:], ck[q + "w3.scale"]) and torch.equal(full["experts.w2"][e], ck[q + "w2.weight"].view(torch.uint8))
+    assert load.shard_bounds(E, 4) == [(0, 1), (1, 2), (3, 1), (4, 2)] and load.shard_bounds(E, 3, [1, 2, 3]) == [(0, 1), (1, 2), (3, 3)]
+    with pytest.raises(ValueError):
+        load.shard_bounds(E, 3, [1, 2, 2])
+    ep = [("cpu", s, n) for s, n in load.shard_bounds(E, 3)]
+    sharded = load.load_experts(ck, p, "cpu", ep=ep)
+    assert [(sh["start"], sh["n"]) for sh in sharded["experts.ep"]] == [(0, 2), (2, 2), (4, 2)]
+    for sh in sharded["experts.ep"]:
+        for k in ("w13", "s13", "w2", "s2"):
+            assert torch.equal(sh[k], full["experts." + k][sh["start"]:sh["start"] + sh["n"]])
+    assert sharded["experts.w13"] is sharded["experts.ep"][0]["w13"]
 
 
 def test_w8_permutation_and_dequant(mods):
