@@ -18,6 +18,7 @@ namespace b200 {
 int p2p_device_error(int* out);  // p2p.cu
 
 constexpr int ROUTE_THREADS = 128;
+static_assert(ROUTE_THREADS == GATE_BLOCK_THREADS, "the block router is written for the routing kernels' block size");
 constexpr int ROUTE_MAX_PAIRS = 4096;   // pairs the single-block bucketing handles
 constexpr int ROUTE_MAX_EXPERTS = 1024;
 constexpr int MX_AUTO_MIN_TOKENS = 0;   // automatic engine choice: the tensor-core kernels serve every batch size whose formats they accept
@@ -215,7 +216,7 @@ struct DqRouteArgs {
 };
 
 __global__ void __launch_bounds__(ROUTE_THREADS) dq_route_kernel(const DqRouteArgs a) {
-    __shared__ float s_val[ROUTE_MAX_EXPERTS], s_key[ROUTE_MAX_EXPERTS];
+    __shared__ GateBlockSmem s_gate;
     __shared__ float s_raw[ROUTE_MAX_EXPERTS];
     __shared__ int s_widx[ROUTE_MAX_EXPERTS];
     __shared__ int s_wtot[ROUTE_THREADS / 32];
@@ -273,17 +274,19 @@ __global__ void __launch_bounds__(ROUTE_THREADS) dq_route_kernel(const DqRouteAr
             a.eid[(long)tok * a.topk + tid] = __ldg(a.eid_in + (long)tok * a.topk + tid);
             a.wt[(long)tok * a.topk + tid] = __ldg(a.wt_in + (long)tok * a.topk + tid);
         }
-    } else if (warp == 0) {
+    } else {
         const float* row_f32 = a.logit_parts > 0 ? s_raw : (a.logits_f32 ? a.logits_f32 + (long)tok * a.logits_ld : nullptr);
-        gate_topk_warp(row_f32, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E, a.temp, a.topk, a.route_scale, a.mode, a.norm,
-                       a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_val, s_key);
+        gate_topk_block(row_f32, a.logits_bf16 ? a.logits_bf16 + (long)tok * a.logits_ld : nullptr, a.bias, a.E, a.temp, a.topk, a.route_scale, a.mode, a.norm,
+                        a.eid + (long)tok * a.topk, a.wt + (long)tok * a.topk, s_gate);
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) is_last = (atomicInc(a.counter, gridDim.x - 1) == gridDim.x - 1);
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
+    if (gridDim.x > 1) {  // a single token needs no election (and the host skips clearing the counter)
+        if (tid == 0) is_last = (atomicInc(a.counter, gridDim.x - 1) == gridDim.x - 1);
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+    }
 
     const int P = a.tokens * a.topk, E = a.E;
     for (int e = tid; e < E; e += ROUTE_THREADS) s_widx[e] = 0;
@@ -705,7 +708,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         r.shard_start = m->shard_start; r.shard_n = shard_n;
         r.eid = w.eid; r.wt = w.wt; r.x8 = w.x8t; r.x_atoms = w.dq_x_atoms; r.work = w.dq_work; r.n_work = w.n_work; r.slot = w.dq_slot; r.pair_work = w.dq_pair_work;
         r.counter = w.counter; r.flags = w.dq_flags; r.n_flags = 2 * DQ_MAX_CTAS;
-        if ((ce = cudaMemsetAsync(w.counter, 0, sizeof(unsigned int), stream)) != cudaSuccess) return (int)ce;
+        if (T > 1 && (ce = cudaMemsetAsync(w.counter, 0, sizeof(unsigned int), stream)) != cudaSuccess) return (int)ce;
         dq_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
         B200_CHECK_LAUNCH();
         const long long MW = (long long)dq_max_works((size_t)P);
