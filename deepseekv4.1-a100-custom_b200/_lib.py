@@ -58,6 +58,11 @@ _SIGNATURES = {
     "b200_hc_pre_norm_quant2": (c_i, [c_p, c_p, c_p, c_i, c_f, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
     "b200_hc_post2": (c_i, [c_p, c_p, c_p, c_ll, c_ll, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_p]),
     "b200_device_error": (c_i, [c_p, c_p]),
+    "b200_fp8_gemm_auto_workspace_bytes": (c_sz, [c_i, c_i]),
+    "b200_fp8_gemm_auto": (c_i, [c_p, c_ll, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_i, c_ll, c_p, c_sz, c_p]),
+    "b200_fp4_grouped_auto_workspace_bytes": (c_sz, [c_i, c_i]),
+    "b200_fp4_grouped_gemm_auto": (c_i, [c_p, c_ll, c_i, c_p, c_ll, c_p, c_ll, c_i, c_i, c_i, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_ll,
+                                         c_p, c_sz, c_p]),
     "b200_p2p_copy": (c_i, [c_p, c_p, c_ll, c_p]),
     "b200_p2p_copy_row": (c_i, [c_p, c_p, c_p, c_ll, c_i, c_ll, c_p, c_p]),
     "b200_p2p_signal": (c_i, [c_p, c_i, c_p, c_p]),

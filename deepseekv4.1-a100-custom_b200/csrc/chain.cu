@@ -925,6 +925,110 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     return 0;
 }
 
+// ------------------------------------------------------------------ the reference-named GEMMs on the block-scaled tensor cores when that is exact
+// The reference's launchers take a bf16 activation.  Inside the MoE layer that tensor is always an FP8 fake-quantised one, i.e. exactly
+// e4m3 values times a power of two per group of 32, which is what the block-scaled tensor cores multiply; elsewhere it need not be.
+// The *_auto entry points find out ON THE DEVICE: they quantise the activation, compare it with the original, and launch the tensor-core
+// kernel and the weight-streaming kernel both tied to the outcome, so exactly one of them does the work.  No host synchronisation; the
+// result is the reference's in either case.
+extern "C" size_t b200_fp8_gemm_auto_workspace_bytes(int M, int K) {
+    if (M < 0 || K < 0) return 0;
+    return rnd256((size_t)(M + 128) * K) + rnd256((size_t)(M + 128) * (K / 32)) + 512;
+}
+
+extern "C" int b200_fp8_gemm_auto(const void* x, long long x_ld, int M, const void* w8_natural, const void* w8_permk, const void* s, int s_cols, int N, int K,
+                                  void* out, int out_is_f32, long long out_ld, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!x || (!w8_natural && !w8_permk) || !s || !out || M < 0) return ERR_BAD_ARG;
+    if (M == 0) return 0;
+    const bool mx_ok = w8_natural && K % 128 == 0 && M > SK_TOK && workspace && !((uintptr_t)workspace & 255) &&
+                       workspace_bytes >= b200_fp8_gemm_auto_workspace_bytes(M, K) && !((uintptr_t)x & 15) && x_ld % 8 == 0;
+    const void* wstream = w8_permk ? w8_permk : w8_natural;
+    if (!mx_ok) return b200_fp8_gemm(x, x_ld, M, wstream, s, SK_FMT_FP8_E8M0, s_cols, w8_permk ? 1 : 0, N, K, out, out_is_f32, out_ld, stream);
+    Carver cv{(char*)workspace, workspace_bytes};
+    uint8_t* q8 = cv.take<uint8_t>((size_t)(M + 128) * K);
+    uint8_t* sf = cv.take<uint8_t>((size_t)(M + 128) * (K / 32));
+    int* exact = cv.take<int>(1);
+    if (!cv.ok) return ERR_WORKSPACE;
+    int rc = mx_quantize_rows_check((const __nv_bfloat16*)x, x_ld, nullptr, M, K, q8, sf, exact, stream);
+    if (rc) return rc;
+    MxArgs a{};
+    MxProb& q = a.p[0];
+    a.n_prob = 1;
+    q.w = w8_natural; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
+    q.s = (const uint8_t*)s; q.s_rstride = s_cols; q.s_row_shift = 5;
+    q.N = N; a.K = K; q.x8 = q8; q.x8_rows = M + 128; q.xsf = sf; q.xsf_ld = K / 32;
+    a.nd = M > 64 ? 128 : 64; a.rows_a = 256; a.kb = 4;
+    q.epi = out_is_f32 ? MX_EPI_STORE_F32 : MX_EPI_STORE_BF16; q.out = out; q.out_ld = out_ld;
+    q.work = nullptr; q.dense_rows = M; q.n_work_host = (M + a.nd - 1) / a.nd;
+    a.run_if = exact; a.run_if_nonzero = 1;
+    if ((rc = mx_launch(a, stream))) return rc;
+    SkinnyArgs k{};
+    k.w = (const uint8_t*)wstream; k.s = (const uint8_t*)s; k.s_rstride = s_cols;
+    k.N = N; k.K = K; k.x = (const __nv_bfloat16*)x; k.x_ld = x_ld; k.w_permk = w8_permk ? 1 : 0;
+    k.work = nullptr; k.dense_rows = M; k.n_work_host = (M + SK_TOK - 1) / SK_TOK;
+    k.out = out; k.out_ld = out_ld;
+    k.run_if = exact; k.run_if_nonzero = 0;
+    return skinny_launch(k, SK_FMT_FP8_E8M0, out_is_f32 ? SK_EPI_STORE_F32 : SK_EPI_STORE_BF16, stream);
+}
+
+extern "C" size_t b200_fp4_grouped_auto_workspace_bytes(int n_pairs, int K) {
+    if (n_pairs < 0 || K < 0) return 0;
+    return 2 * rnd256((size_t)(n_pairs + 1) * sizeof(int4)) + rnd256((size_t)(n_pairs + 128) * K) + rnd256((size_t)(n_pairs + 128) * (K / 32)) + 1024;
+}
+
+extern "C" int b200_fp4_grouped_gemm_auto(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s, long long s_estride, int n_local_experts,
+                                          int N, int K, const int* grp_expert, const int* grp_start, const int* grp_count, int n_groups, const int* pair_tok,
+                                          const int* pair_out, const float* pair_w, int n_pairs, int shard_start, int shard_n, int zero_out, int accumulate,
+                                          float* out, long long out_ld, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!x || !w || !s || !grp_expert || !grp_start || !out || !workspace || n_groups < 0 || n_pairs < 0 || n_local_experts < 1) return ERR_BAD_ARG;
+    if (workspace_bytes < b200_fp4_grouped_auto_workspace_bytes(n_pairs, K) || ((uintptr_t)workspace & 255)) return ERR_WORKSPACE;
+    if (K % 128 || ((uintptr_t)x & 15) || x_ld % 8 || ((uintptr_t)w & 31) || (w_estride & 31)) return ERR_BAD_ALIGN;
+    if (n_pairs == 0 || n_groups == 0) return 0;
+    Carver cv{(char*)workspace, workspace_bytes};
+    int4* work_mx = cv.take<int4>((size_t)n_pairs + 1);
+    int4* work_sk = cv.take<int4>((size_t)n_pairs + 1);
+    uint8_t* q8 = cv.take<uint8_t>((size_t)(n_pairs + 128) * K);
+    uint8_t* sf = cv.take<uint8_t>((size_t)(n_pairs + 128) * (K / 32));
+    int* n_work_mx = cv.take<int>(1);
+    int* n_work_sk = cv.take<int>(1);
+    int* exact = cv.take<int>(1);
+    if (!cv.ok) return ERR_WORKSPACE;
+    if (shard_n > n_local_experts) shard_n = n_local_experts;
+    int rc;
+    if (zero_out && !accumulate &&
+        (rc = skinny_zero_foreign(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, pair_out, out, out_ld, N, stream)))
+        return rc;
+    // activation rows gathered into pair order, quantised, checked
+    if ((rc = mx_quantize_rows_check((const __nv_bfloat16*)x, x_ld, pair_tok, n_pairs, K, q8, sf, exact, stream, x_perm8))) return rc;
+    // ---- tensor-core kernel, if the activation was FP8-exact
+    const int nd = 64;
+    if ((rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, work_mx, n_work_mx, n_pairs, stream, nd))) return rc;
+    MxArgs a{};
+    MxProb& q = a.p[0];
+    a.n_prob = 1;
+    q.w = w; q.w_estride = w_estride; q.n_experts = n_local_experts; q.a_fmt = MX_A_E2M1;
+    q.s = (const uint8_t*)s; q.s_estride = s_estride; q.s_rstride = K / 32; q.s_row_shift = 0;
+    q.N = N; a.K = K; q.x8 = q8; q.x8_rows = n_pairs + 128; q.xsf = sf; q.xsf_ld = K / 32;
+    a.nd = nd; a.rows_a = 256; a.kb = 4;
+    q.epi = accumulate ? MX_EPI_ATOMIC_F32 : MX_EPI_STORE_F32;
+    q.pair_out = pair_out; q.pair_w = pair_w; q.out = out; q.out_ld = out_ld;
+    q.work = work_mx; q.n_work = n_work_mx;
+    a.run_if = exact; a.run_if_nonzero = 1;
+    if ((rc = mx_launch(a, stream))) return rc;
+    // ---- weight-streaming kernel otherwise
+    SkinnyArgs k{};
+    k.w = (const uint8_t*)w; k.w_estride = w_estride; k.n_experts = n_local_experts;
+    k.s = (const uint8_t*)s; k.s_estride = s_estride; k.s_rstride = K / 32;
+    k.N = N; k.K = K; k.x = (const __nv_bfloat16*)x; k.x_ld = x_ld; k.x_perm8 = x_perm8;
+    k.work = work_sk; k.n_work = n_work_sk; k.pair_tok = pair_tok; k.pair_out = pair_out; k.pair_w = pair_w;
+    k.out = out; k.out_ld = out_ld;
+    k.run_if = exact; k.run_if_nonzero = 0;
+    const int epi = accumulate ? SK_EPI_ATOMIC_F32 : SK_EPI_STORE_F32;
+    if ((rc = skinny_check(k, SK_FMT_FP4_E8M0, epi))) return rc;
+    if ((rc = skinny_plan(grp_expert, grp_start, grp_count, n_groups, n_pairs, shard_start, shard_n, work_sk, n_work_sk, n_pairs, stream))) return rc;
+    return skinny_launch(k, SK_FMT_FP4_E8M0, epi, stream);
+}
+
 // ------------------------------------------------------------------ load-time re-layout of the scales
 extern "C" size_t b200_scale_atoms_bytes(int n_experts, int N, int K, int dual) { return scale_atoms_bytes(n_experts, N, K, dual); }
 

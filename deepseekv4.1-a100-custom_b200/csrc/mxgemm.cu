@@ -97,7 +97,9 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
     const int ipw1 = a.n_prob > 1 ? ((a.dual ? a.inter : a.p[1].N) + rows_w - 1) / rows_w : 1;
     const long items0 = (long)(a.p[0].n_work ? *a.p[0].n_work : a.p[0].n_work_host) * ipw0;
     const long items1 = a.n_prob > 1 ? (long)(a.p[1].n_work ? *a.p[1].n_work : a.p[1].n_work_host) * ipw1 : 0;
-    const long total = items0 + items1;
+    // a launch may be tied to a device-side condition (run_if in mxgemm.cuh): when it does not hold there are no items
+    const bool skip = a.run_if && ((*a.run_if != 0) != (a.run_if_nonzero != 0));
+    const long total = skip ? 0 : items0 + items1;
     const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
     const int n_acc = (2 * NW <= MX_ACC_COLS_MAX) ? 2 : 1;  // two accumulator buffers (epilogue overlaps the next item) when they fit
     const uint32_t sf_col0 = (uint32_t)(n_acc * NW);        // the scale columns follow the accumulators
@@ -524,6 +526,58 @@ __global__ void __launch_bounds__(256) mx_quantize_rows_vec_kernel(const __nv_bf
     if ((c8 & 3) == 0) so[(long)row * (K >> 5) + (c8 >> 2)] = (uint8_t)sb;
 }
 
+// The same quantisation with a check: `exact` (a device word the caller sets non-zero) is cleared when some value of x is NOT
+// reproduced by its quantised form, i.e. when x was not already an FP8 fake-quantised tensor.  Inside the MoE layer the activations
+// always are (dsv41/model.py:2040, dsv41/fused.py:297-306), which is what lets a caller that only has the bf16 tensor use the
+// block-scaled tensor cores without changing a single output bit; launches that follow can be tied to the word (run_if).
+// x_perm8: x is stored in the reference's 8-k permuted order (slot j of every 8 holds k = bit reversal of j, dsv41/cukern.py:267-273); a
+// thread's 8 values are one such group, put back in natural order here.
+__global__ void __launch_bounds__(256) mx_quantize_rows_check_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, const int* __restrict__ src_row, int rows,
+                                                                     int K, uint8_t* __restrict__ q8, uint8_t* __restrict__ sf, int* __restrict__ exact, int x_perm8) {
+    const int tpr = K >> 3;
+    const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool on = gid < (long)rows * tpr;
+    const int row = on ? (int)(gid / tpr) : 0, c8 = on ? (int)(gid % tpr) : 0;
+    const long src = src_row ? __ldg(src_row + row) : row;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (on) raw = __ldg(reinterpret_cast<const uint4*>(x + src * x_ld) + c8);
+    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+    float v[8], amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[2 * i] = bf16_bits_to_f32(u[i] & 0xFFFFu);
+        v[2 * i + 1] = bf16_bits_to_f32(u[i] >> 16);
+        amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+    }
+    if (x_perm8) {
+        float t = v[1]; v[1] = v[4]; v[4] = t;
+        t = v[3]; v[3] = v[6]; v[6] = t;
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!on) return;
+    const float sc = fp8_group_scale_bf16(amax);
+    const uint32_t sb = (f32_as_u32(sc) >> 23) & 0xFFu;
+    const float inv = u32_as_f32((254u - sb) << 23);
+    uint32_t o[2];
+    bool same = true;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t w = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float qv = fminf(fmaxf(v[4 * h + e] * inv, -448.f), 448.f);
+            const __nv_fp8_storage_t code = __nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3);
+            w |= (uint32_t)code << (8 * e);
+            same = same && (__half2float(__half(__nv_cvt_fp8_to_halfraw(code, __NV_E4M3))) * sc == v[4 * h + e]);
+        }
+        o[h] = w;
+    }
+    *reinterpret_cast<uint2*>(q8 + (long)row * K + c8 * 8) = make_uint2(o[0], o[1]);
+    if ((c8 & 3) == 0) sf[(long)row * (K >> 5) + (c8 >> 2)] = (uint8_t)sb;
+    if (!same) *exact = 0;
+}
+
 // ------------------------------------------------------------------ host side
 int sm_count();
 
@@ -649,6 +703,19 @@ int mx_device_error(int* out, cudaStream_t stream) {
         cudaMemcpyToSymbol(g_mx_error, &z, sizeof(int));
     }
     *out = v;
+    return 0;
+}
+
+int mx_quantize_rows_check(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, int* exact, cudaStream_t stream,
+                           int x_perm8) {
+    if (!x || !q8 || !sf || !exact || rows < 0 || K <= 0 || K % 32) return ERR_BAD_ARG;
+    if (((uintptr_t)x & 15) || x_ld % 8 || ((uintptr_t)q8 & 7)) return ERR_BAD_ALIGN;
+    cudaError_t e = cudaMemsetAsync(exact, 1, sizeof(int), stream);  // non-zero: "exact so far"
+    if (e != cudaSuccess) return (int)e;
+    if (rows == 0) return 0;
+    const long threads = (long)rows * (K / 8);
+    mx_quantize_rows_check_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(x, x_ld, src_row, rows, K, q8, sf, exact, x_perm8);
+    B200_CHECK_LAUNCH();
     return 0;
 }
 

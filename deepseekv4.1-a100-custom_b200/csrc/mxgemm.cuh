@@ -62,9 +62,14 @@ struct MxArgs {
     int stg_rows;           // token rows of the small-tile staging buffer (set by mx_launch): works up to this size take the staged epilogue
     float limit;
     int inter;
+    const int* run_if;      // optional device word: the launch does its work only if (*run_if != 0) == (run_if_nonzero != 0)
+    int run_if_nonzero;
 };
 
 int mx_launch(const MxArgs& a, cudaStream_t stream);
+// quantise as mx_quantize_rows and clear *exact (set non-zero first, on the stream) if x is not reproduced exactly by its quantised form
+int mx_quantize_rows_check(const __nv_bfloat16* x, long long x_ld, const int* src_row, int rows, int K, uint8_t* q8, uint8_t* sf, int* exact, cudaStream_t stream,
+                           int x_perm8 = 0);
 int mx_device_error(int* out, cudaStream_t stream);  // copies and clears the device error word (synchronises the stream)
 
 // bf16 [rows][K] -> e4m3 bytes + E8M0 scale byte per 32 (the FP8 fake quantisation of dsv41/quant.py:46-54 kept in

@@ -126,6 +126,12 @@ extern "C" int b200_group_pairs(const int* expert, const int* row_in, const int*
     cudaError_t ce;
     if ((ce = cudaMemsetAsync(cnt, 0, sizeof(int) * n_experts, stream)) != cudaSuccess) return (int)ce;
     if (n_pairs > 0) {
+        // pairs with an id outside the expert range are dropped: the slots they leave unused at the end of the sorted arrays hold row 0 /
+        // weight 0, so that a kernel that walks all n_pairs slots (a row gather) stays inside its tensors
+        int* const i32[4] = {order, s_expert, s_row_in, s_row_out};
+        for (int* p : i32)
+            if ((ce = cudaMemsetAsync(p, 0, sizeof(int) * (size_t)n_pairs, stream)) != cudaSuccess) return (int)ce;
+        if ((ce = cudaMemsetAsync(s_weight, 0, sizeof(float) * (size_t)n_pairs, stream)) != cudaSuccess) return (int)ce;
         gp_hist_kernel<<<(n_pairs + 255) / 256, 256, 0, stream>>>(expert, n_pairs, n_experts, cnt);
         B200_CHECK_LAUNCH();
     }

@@ -151,7 +151,9 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
     const int nst = (int)((wrow_bytes + SK_STAGE_ROW_BYTES - 1) / SK_STAGE_ROW_BYTES);  // stages per item
     const int n_units = K >> 5;                                                         // activation units per token column
     const int ipw = (EPI == SK_EPI_SWIGLU) ? (a.inter >> 5) : ((N + SK_ROWS - 1) / SK_ROWS);
-    const int n_work = a.n_work ? *a.n_work : a.n_work_host;
+    // a launch may be tied to a device-side condition (see run_if in skinny.cuh): when it does not hold the kernel has nothing to do
+    const bool skip = a.run_if && ((*a.run_if != 0) != (a.run_if_nonzero != 0));
+    const int n_work = skip ? 0 : (a.n_work ? *a.n_work : a.n_work_host);
     const long total = (long)n_work * ipw;
     const long lo = total * blockIdx.x / gridDim.x, hi = total * (blockIdx.x + 1) / gridDim.x;
 

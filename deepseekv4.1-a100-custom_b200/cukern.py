@@ -10,6 +10,7 @@ from . import _lib as L
 
 _PERM8 = [0, 4, 2, 6, 1, 5, 3, 7]
 FP4_W_MAX = 64  # tokens per group the reference's bucketing produces (dsv41/cukern.py:276-277); any size is accepted here
+AUTO_ENGINE = True  # grouped FP4 / dense FP8 GEMMs pick the tensor-core kernel on the device when the activation is FP8-exact (tests switch it off)
 
 
 def _i32(t: torch.Tensor | None, dev) -> torch.Tensor | None:
@@ -44,11 +45,24 @@ def grouped_fp4(x, w, s, grp_expert, grp_start, grp_count, pair_tok, pair_out, p
     G = ge.numel()
     assert gs.numel() >= (G if gc is not None else G + 1)
     lib = L.lib()
+    fmt = _fp4_fmt(s)
+    if fmt == L.FMT_FP4_E8M0 and K % 128 == 0 and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0 and AUTO_ENGINE:
+        # engine chosen on the device: the block-scaled tensor cores when the activation is FP8-exact (inside the MoE it always is), else
+        # the weight-streaming kernel
+        nbytes = lib.b200_fp4_grouped_auto_workspace_bytes(int(n_pairs), K)
+        ws = L.workspace(dev, nbytes, "fp4_grouped_auto")
+        with torch.cuda.device(dev):
+            rc = lib.b200_fp4_grouped_gemm_auto(L.ptr(x), x.stride(0), int(bool(x_perm8)), L.ptr(w), w.stride(0) * w.element_size(), L.ptr(s), s.stride(0) * s.element_size(), E, N, K,
+                                                L.ptr(ge), L.ptr(gs), L.ptr(gc), G, L.ptr(pt), L.ptr(po), L.ptr(pw), int(n_pairs), int(shard_start),
+                                                int(min(shard_n, 1 << 30)), int(bool(zero_out)), int(bool(accumulate)), L.ptr(out), out.stride(0), L.ptr(ws),
+                                                ws.numel(), L.stream_of(dev))
+        L.check(rc, "b200_fp4_grouped_gemm_auto")
+        return out
     nbytes = lib.b200_fp4_grouped_workspace_bytes(int(n_pairs))
     ws = L.workspace(dev, nbytes, "fp4_grouped")
     with torch.cuda.device(dev):
         rc = lib.b200_fp4_grouped_gemm(L.ptr(x), x.stride(0), int(bool(x_perm8)), L.ptr(w), w.stride(0) * w.element_size(), L.ptr(s),
-                                       s.stride(0) * s.element_size(), _fp4_fmt(s), E, N, K, L.ptr(ge), L.ptr(gs), L.ptr(gc), G, L.ptr(pt), L.ptr(po),
+                                       s.stride(0) * s.element_size(), fmt, E, N, K, L.ptr(ge), L.ptr(gs), L.ptr(gc), G, L.ptr(pt), L.ptr(po),
                                        L.ptr(pw), int(n_pairs), int(shard_start), int(min(shard_n, 1 << 30)), int(bool(zero_out)),
                                        int(bool(accumulate)), L.ptr(out), out.stride(0), L.ptr(ws), ws.numel(), L.stream_of(dev))
     L.check(rc, "b200_fp4_grouped_gemm")
@@ -118,11 +132,35 @@ def _fp8(x, w8, s8, w_permk: bool, out_dtype, out=None):
     if out is None:
         out = torch.empty(M, N, device=dev, dtype=out_dtype)
     assert out.dtype == out_dtype and out.stride(-1) == 1
+    lib = L.lib()
+    if fmt == L.FMT_FP8_E8M0 and M > 8 and K % 128 == 0 and AUTO_ENGINE and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0:
+        # more than 8 rows: the tensor-core kernel reads the weights once (the streaming kernel once per 8 rows); it needs the weight bytes
+        # in natural k order, kept beside a permuted tensor the first time it is used this way
+        nat = w8 if not w_permk else _natural_copy(w8)
+        ws = L.workspace(dev, lib.b200_fp8_gemm_auto_workspace_bytes(M, K), "fp8_auto")
+        with torch.cuda.device(dev):
+            rc = lib.b200_fp8_gemm_auto(L.ptr(x), x.stride(0), M, L.ptr(nat), L.ptr(w8) if w_permk else None, L.ptr(s8), s8.shape[1], N, K, L.ptr(out),
+                                        int(out_dtype == torch.float32), out.stride(0), L.ptr(ws), ws.numel(), L.stream_of(dev))
+        L.check(rc, "b200_fp8_gemm_auto")
+        return out
     with torch.cuda.device(dev):
-        rc = L.lib().b200_fp8_gemm(L.ptr(x), x.stride(0), M, L.ptr(w8), L.ptr(s8), fmt, s8.shape[1], int(bool(w_permk)), N, K, L.ptr(out),
-                                   int(out_dtype == torch.float32), out.stride(0), L.stream_of(dev))
+        rc = lib.b200_fp8_gemm(L.ptr(x), x.stride(0), M, L.ptr(w8), L.ptr(s8), fmt, s8.shape[1], int(bool(w_permk)), N, K, L.ptr(out),
+                               int(out_dtype == torch.float32), out.stride(0), L.stream_of(dev))
     L.check(rc, "b200_fp8_gemm")
     return out
+
+
+_natural: dict = {}
+
+
+def _natural_copy(w8_permk: torch.Tensor) -> torch.Tensor:
+    """Natural-k-order twin of a weight stored in the 16-k order of dsv41/w8.py:21-23 (made once per weight)."""
+    key = (w8_permk.data_ptr(), tuple(w8_permk.shape), w8_permk.device)
+    t = _natural.get(key)
+    if t is None:
+        from .w8 import unpermute_k
+        t = _natural[key] = unpermute_k(w8_permk)
+    return t
 
 
 def fp8_gemv(x: torch.Tensor, w_fp8: torch.Tensor, s_u8: torch.Tensor) -> torch.Tensor:

@@ -91,7 +91,7 @@ int b200_permute_x8(const void* x, void* y, long long n_elems, cudaStream_t stre
  *   grp_expert int32 [n_groups] (global ids, -1 = padding); group g owns pairs grp_start[g] .. +count-1 with count =
  *   grp_count[g], or grp_start[g+1] - grp_start[g] when grp_count is NULL (then grp_start has n_groups+1 entries,
  *   dsv41/decode.py:431-432; the grp_count form is the tile table of dsv41/moe_kernels.py:118-132); pair_tok / pair_out int32
- *   [n_pairs] or NULL (= pair index); pair_w fp32 [n_pairs] or NULL; out fp32, row stride out_ld elements.
+ *   [n_pairs] or NULL (= pair index), EVERY entry a valid row (also those of pairs no group covers: the auto form gathers them all); pair_w fp32 [n_pairs] or NULL; out fp32, row stride out_ld elements.
  *   Groups whose expert is outside [shard_start, shard_start + shard_n) are skipped; with zero_out their rows are
  *   zeroed (dsv41/cuda/fp4_tc.cu:66-72).  K % 128 == 0, N % 16 == 0, K <= 9088.  Groups of any size are accepted;
  *   more than 8 pairs re-read the expert once per 8.
@@ -141,6 +141,24 @@ int b200_regroup_pairs(const int* order, int n_pairs, const int* row_in, const i
  *   are read once per 8 rows. */
 int b200_fp8_gemm(const void* x, long long x_ld, int M, const void* w8, const void* s, int fmt, int s_cols, int w_permk, int N, int K, void* out,
                   int out_is_f32, long long out_ld, cudaStream_t stream);
+
+/* ---- the two GEMMs above with the engine chosen ON THE DEVICE.  The activation is quantised to FP8 (e4m3 + E8M0 per 32) and compared with
+ * the original; if it is reproduced exactly (it always is inside the MoE layer, dsv41/model.py:2040, dsv41/fused.py:297-306) the
+ * block-scaled tensor-core kernel (tcgen05) computes the result, otherwise the weight-streaming kernel does: both are launched, tied to the
+ * outcome word, and one of them finds nothing to do.  Same results as the plain entry points, no host synchronisation, E8M0 scale formats.
+ *   b200_fp8_gemm_auto: w8_natural = weight bytes in natural k order (needed by the tensor cores; NULL: streaming only), w8_permk = the same
+ *   weights in the 16-k order of dsv41/w8.py:21-23 (or NULL); rows M <= 8 always stream.  Replaces linear_w / fp8_gemm_tc for any row
+ *   count (dsv41/w8.py:64-83, dsv41/cukern.py:165-252): a 512-row call reads the weights once, not once per 8 rows.
+ *   b200_fp4_grouped_gemm_auto: arguments of b200_fp4_grouped_gemm (E8M0 scales).  Replaces grouped_fp4_gemm
+ *   (dsv41/moe_kernels.py:161-231) and fp4_gemv_pairs.  Workspaces: the *_workspace_bytes functions, 256-byte aligned. */
+size_t b200_fp8_gemm_auto_workspace_bytes(int M, int K);
+int b200_fp8_gemm_auto(const void* x, long long x_ld, int M, const void* w8_natural, const void* w8_permk, const void* s, int s_cols, int N, int K, void* out,
+                       int out_is_f32, long long out_ld, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t b200_fp4_grouped_auto_workspace_bytes(int n_pairs, int K);
+int b200_fp4_grouped_gemm_auto(const void* x, long long x_ld, int x_perm8, const void* w, long long w_estride, const void* s, long long s_estride, int n_local_experts, int N,
+                               int K, const int* grp_expert, const int* grp_start, const int* grp_count, int n_groups, const int* pair_tok, const int* pair_out,
+                               const float* pair_w, int n_pairs, int shard_start, int shard_n, int zero_out, int accumulate, float* out, long long out_ld,
+                               void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 /* ---- whole MoE layer for a decode batch: router -> input fake quantisation -> routed FP4 experts (gate/up, SwiGLU
  * with routing weight, FP8 fake quantisation, down) -> shared FP8 expert -> combine.  Replaces, in one call, the

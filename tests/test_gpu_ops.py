@@ -351,3 +351,49 @@ def test_loader_relayout_and_layer_from_shard(mods, oracle, dev):
     routed = layer.forward(x.to(dev), logits.to(dev), final=False, want_routed=True)
     ref = oracle.moe_layer(x, logits.float(), None, ex["w13"][2:6], ex["s13"][2:6], ex["w2"][2:6], ex["s2"][2:6], None, topk=topk, shard=(2, 4), n_experts=E)
     assert rel_err(routed, ref["routed"]) <= 2e-3
+
+
+@pytest.mark.parametrize("exact", [True, False])
+def test_reference_named_launchers_choose_the_engine_on_the_device(mods, oracle, dev, exact):
+    """grouped_fp4_gemm / fp4_gemm_tc / linear_w with an FP8-exact activation run the tcgen05 kernels, with any other bf16 activation the
+    streaming kernels; both match the checker, and an inexact activation gives the streaming kernels' bits."""
+    ck = mods.cukern
+    E, N, K, M, topk = 8, 512, 1024, 300, 2
+    w, s, g = _experts(E, N, K, 555, 112, 128)
+    a = (torch.randn(M, K, generator=g) * 2).to(torch.bfloat16)
+    if exact:
+        a = oracle.fake_quant_fp8(a, 32)
+    eid = torch.randint(0, E, (M, topk), generator=g)
+    wt = torch.rand(M, topk, generator=g)
+    row = torch.arange(M).repeat_interleave(topk)
+    ref = oracle.fp4_pairs(a, w, s, eid.flatten(), row, row, wt.flatten(), M)
+    pairs = mods.moe_kernels.GroupedPairs(eid.flatten().to(dev), row.to(dev), row.clone().to(dev), wt.flatten().to(dev), block_m=64, n_experts=E)
+    got = mods.moe_kernels.grouped_fp4_gemm(a.to(dev), w.to(dev), s.to(dev), pairs, M)
+    assert rel_err(got, ref) < 2e-3 and ck.device_error(dev) == 0
+    ck.AUTO_ENGINE = False
+    try:
+        streaming = mods.moe_kernels.grouped_fp4_gemm(a.to(dev), w.to(dev), s.to(dev), pairs, M)
+    finally:
+        ck.AUTO_ENGINE = True
+    assert rel_err(streaming, ref) < 2e-3
+    # 8-k permuted activation (fp4_gemm_tc): one group per expert
+    order = torch.argsort(eid[:, 0], stable=True)
+    experts, counts = torch.unique(eid[order, 0], return_counts=True)
+    gs = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)]).int()
+    ref_tc = oracle.fp4_pairs(a, w, s, eid[order, 0], order, torch.arange(M), None, M)
+    y = ck.fp4_gemm_tc(ck.permute_x(a.to(dev)), w.to(dev), s.to(dev), experts.int().to(dev), gs.to(dev), order.int().to(dev), M, 64)
+    assert rel_err(y, ref_tc) < 2e-3
+    # dense FP8, more than 8 rows
+    w8, s8 = _rand_fp8(768, K, g)
+    W = mods.w8.W8(w8.to(dev), s8.to(dev))
+    ref8 = oracle.fp8_gemm(a, w8, s8)
+    y8 = mods.w8.linear_w(a.to(dev), W)
+    assert y8.shape == (M, 768) and rel_err(y8, ref8) < 1e-2
+    ck.AUTO_ENGINE = False
+    try:
+        y8s = mods.w8.linear_w(a.to(dev), W)
+    finally:
+        ck.AUTO_ENGINE = True
+    if not exact:  # nothing but the streaming kernel may have written the result
+        assert torch.equal(got, streaming) and torch.equal(y8, y8s)
+    assert ck.device_error(dev) == 0
