@@ -626,7 +626,7 @@ def run_gpu(args):
                                    "avg_launch_ms": k_ms, "achieved": f1 / (k_ms * 1e-3) / 1e12, "frac": f1 / (k_ms * 1e-3) / 1e12 / tpeak}
         return r
 
-    S_PRE = 4096
+    S_PRE = WORKLOADS["prefill4096"]
     if S <= 64:
         mx = layer._use_mx(S)
         # the tensor-core launch streams the shared expert's gate/up matrix (FP8 + 32x32 scales) in the same kernel
