@@ -1,12 +1,13 @@
 // Weight-streaming grouped "skinny" GEMM for decode: out[pair, n] = sum_k x[tok(pair), k] * W[expert][n, k] for groups
 // of at most 8 tokens per expert (larger groups are cut into 8-token works that re-read the expert).
 //
-// HBM-bound by design: every weight byte is read exactly once per work with 128-bit streaming loads straight into
-// registers (8 loads of 16 B in flight per lane, 64 KB per SM), dequantised in registers to packed bf16 with the
-// block scale folded into the exponent, and contracted against the (<= 8) token columns with warp-level 16x8x16
-// tensor-core tiles that accumulate in fp32.  One CTA = 16 warps = 4 row blocks of 16 weight rows x 4 splits of K;
-// the K splits are summed through shared memory.  Activations of the work's tokens sit in shared memory in the
-// fragment order of the tile, pre-scaled by 2^ACT_SHIFT.
+// Every weight byte is read once per work: one producer thread streams 32-row x 128-byte boxes of the weight matrix through a
+// shared-memory ring with tensor-map bulk copies (128-byte swizzle) counted on mbarriers; the consumer warps fetch fragments with
+// ldmatrix.x4, dequantise the 32-bit words in registers to packed bf16 with the block scale folded into the exponent, and contract
+// them against the (<= 8) token columns with warp-level 16x8x16 tensor-core tiles that accumulate in fp32.  The K splits of a CTA
+// are summed through shared memory.  Activations of the work's tokens sit in shared memory in the fragment order of the tile,
+// pre-scaled by 2^ACT_SHIFT.  The dequantisation arithmetic, not HBM, bounds the FP4 form (about a quarter of the copy bandwidth);
+// it is the engine for activations or scale formats the block-scaled tensor-core kernels (mxgemm.cu, wmgemm.cu) do not take.
 //
 // Replaces, for the sm_100a build, the reference's sm_80 kernels fp4_gemv_pairs (dsv41/cuda/fp4_gemv.cu:15),
 // fp4_gemv_m1 (dsv41/cuda/fp4_gemv_m1.cu:57), fp4_gemm_tc8/16 (dsv41/cuda/fp4_tc.cu:52), fp8_gemv_m1

@@ -16,8 +16,8 @@
 //     partial accumulator in global memory, the CTA that finishes the tile adds the partial tiles in CTA order (deterministic) before
 //     its epilogue.  A single token touches 6 experts = 112 tiles for 148 SMs; cut by tile a quarter of the machine would idle;
 //   * the accumulator (128 lanes x 256 columns of TMEM) is copied to shared memory by the warps that can read the token lanes and
-//     handed back to the tensor-core issuer at once; all eight epilogue warps then work on (token, 32 columns) tasks of the chosen
-//     pairs, one column per lane, while the next tile's MMAs run.
+//     handed back to the tensor-core issuer at once; all eight epilogue warps then work on (token, 128 columns) tasks of the chosen
+//     pairs with 16-byte accesses while the next tile's MMAs run.
 // Warp roles: warp 0 copy producer, warp 1 TMEM allocation + scale copies (tcgen05.cp) + MMAs, warps 4-11 epilogue.  Every wait is
 // bounded: a wait that runs out of time stores a code in a device error word and the CTA runs on.
 //

@@ -1,5 +1,5 @@
-// Internal interface of the decode-sized block-scaled tensor-core GEMM (wmgemm.cu): weight rows on the M side of the tile, the
-// tokens of the batch (at most 64) on the N side, the k range of the whole launch cut evenly over the CTAs.
+// Internal interface of the decode-sized block-scaled tensor-core GEMM (wmgemm.cu): the tokens of the batch (at most 64) on the
+// M side of the tile, 256 weight rows on the N side, the k range of the whole launch cut evenly over the CTAs.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>

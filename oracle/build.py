@@ -18,7 +18,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "_build", "libmoe_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libmoe_cpu_ref.so")
-DEFAULT_REFERENCE = os.environ.get("B200MOE_REFERENCE_DIR", "/root/reference")
+# the reference checkout: named by the environment, else a directory "reference" beside this repository
+DEFAULT_REFERENCE = os.environ.get("B200MOE_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target: str, *sources: str) -> bool:

@@ -1,8 +1,8 @@
 """Generate the golden vectors of tests/golden/*.pt from the reference checkout.
 
-Run once in a container that has the reference at /root/reference (or pass its path):
+Run once where the reference checkout is at hand:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 What is produced, and from which reference code:
   quant.pt   outputs of the reference's OWN torch definitions, imported from dsv41/quant.py: fake_quant_fp8 (:46-54),
@@ -25,7 +25,9 @@ import torch.nn.functional as F
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/reference")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 
