@@ -434,6 +434,14 @@ def run_gpu(args):
     ls = [l[first:first + T_r].to(dev) for l in ls_h]
     out = torch.empty(T_r, D, device=dev, dtype=torch.bfloat16)
     epl = ep.EPMoE(layer) if world > 1 else None
+    exchange_note = None
+    if world > 1 and S <= 64 and args.exchange != "nccl":
+        # decode steps exchange through this package's own kernels over peer memory; if the slabs cannot be mapped on this box every
+        # rank learns of it together and the step keeps the NCCL collectives
+        try:
+            epl.enable_peer_exchange(64, E, xs[0].dtype, ls[0].dtype)
+        except RuntimeError as e:
+            exchange_note = str(e)[:300]
 
     # ---- parity of one step against the CPU checker (untimed)
     parity = None
@@ -559,7 +567,7 @@ def run_gpu(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(args.workload, world), "clocks": clocks,
             "e2e": {"value": S / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e},
-            "gpu_launches": layer.launches_per_step(T_r * world) * args.steps}
+            "gpu_launches": (layer.launches_per_step(T_r * world) + (4 if world > 1 and epl.peer is not None and S <= epl.peer.max_tokens else 0)) * args.steps}
     if parity is not None:
         line["parity"] = parity
 
@@ -590,6 +598,9 @@ def run_gpu(args):
         if rank == 0:
             gbs = max_rank_bytes / (ms * 1e-3) / 1e9
             line["config"]["cuda_graph"] = bool(graphs.get("resident")) if S <= 64 else False
+            line["config"]["exchange"] = epl.transport(S)
+            if exchange_note:
+                line["config"]["exchange_note"] = exchange_note
             if "error" in graphs:
                 line["config"]["cuda_graph_error"] = graphs["error"]
             line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None, "peak_source": peak_src,
@@ -686,6 +697,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="expert-parallel decode: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel decode: exchange through this package's kernels over peer memory (default), or NCCL all-gather + reduce-scatter")
     ap.add_argument("--engine", type=int, default=0, choices=[0, 1, 2], help="0 automatic, 1 weight-streaming kernels, 2 tcgen05 block-scaled kernels")
     ap.add_argument("--experts", type=int, default=E, help="expert count (smaller than the workload's 384 only for profiler captures)")
     ap.add_argument("--tokens", type=int, default=0, help="token count of the chosen workload (smaller than its own only for profiler captures)")

@@ -33,6 +33,14 @@ class MoeArgs(ctypes.Structure):
                 ("s13_atoms", c_p), ("s2_atoms", c_p), ("sh_s13_atoms", c_p), ("sh_s2_atoms", c_p), ("eid_in", c_p), ("wt_in", c_p)]
 
 
+class EpPeers(ctypes.Structure):
+    """struct b200_ep_peers of include/b200_moe.h."""
+    _fields_ = [("rank", c_i), ("world", c_i), ("dim", c_i), ("x_row_bytes", c_i), ("l_row_bytes", c_i), ("first", c_p), ("inbox_x", c_p),
+                ("inbox_l", c_p), ("flags_in", c_p), ("partials", c_p), ("flags_out", c_p), ("seq", c_p), ("counter", c_p)]
+
+
+EP_MAX_RANKS, EP_HANDLE_BYTES = 16, 64
+
 _SIGNATURES = {
     "b200_version": (c_i, []),
     "b200_error_string": (ctypes.c_char_p, [c_i]),
@@ -72,6 +80,14 @@ _SIGNATURES = {
     "b200_p2p_stamp": (c_i, [c_p, c_p]),
     "b200_memcpy_async": (c_i, [c_p, c_p, c_ll, c_p]),
     "b200_set_wait_limit_ns": (c_i, [ctypes.c_ulonglong]),
+    "b200_ep_dispatch": (c_i, [ctypes.POINTER(EpPeers), c_p, c_p, c_i, c_p]),
+    "b200_ep_return": (c_i, [ctypes.POINTER(EpPeers), c_p, c_i, c_p]),
+    "b200_ep_wait": (c_i, [c_p, c_i, c_p, c_i, c_i, c_p]),
+    "b200_ep_alloc": (c_i, [c_sz, ctypes.POINTER(c_p)]),
+    "b200_ep_free": (c_i, [c_p]),
+    "b200_ep_export": (c_i, [c_p, c_p]),
+    "b200_ep_open": (c_i, [c_p, ctypes.POINTER(c_p)]),
+    "b200_ep_close": (c_i, [c_p]),
     "b200_group_pairs_max_tiles": (c_i, [c_i, c_i, c_i]),
     "b200_group_pairs_workspace_bytes": (c_sz, [c_i]),
     "b200_group_pairs": (c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_sz, c_p]),
@@ -111,6 +127,19 @@ def check(rc: int, what: str) -> None:
 
 def ptr(t) -> ctypes.c_void_p:
     return c_p(t.data_ptr()) if t is not None else c_p(0)
+
+
+class _RawDeviceMemory:
+    """Array-interface view of device memory owned by the library (a slab of b200_ep_alloc), so torch can wrap it without copying."""
+
+    def __init__(self, address: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
+
+
+def tensor_over(address: int, nbytes: int, device) -> torch.Tensor:
+    """uint8 tensor over `nbytes` of device memory at `address`; the caller keeps the memory alive."""
+    with torch.cuda.device(device):
+        return torch.as_tensor(_RawDeviceMemory(address, nbytes), device=device)
 
 
 def stream_of(device) -> ctypes.c_void_p:

@@ -1051,7 +1051,7 @@ extern "C" int b200_device_error(int* code, cudaStream_t stream) {
     int wm = 0, pp = 0;
     if ((rc = wm_device_error(&wm))) return rc;
     if ((rc = p2p_device_error(&pp))) return rc;
-    // prefill tensor-core kernel 11..41, streaming kernels 1001..1091, decode weight-stream kernel 2011..2042, messaging waits 3001..3002
+    // prefill tensor-core kernel 11..41, streaming kernels 1001..1091, decode weight-stream kernel 2011..2042, messaging waits 3001..3004
     *code = mx ? mx : (sk ? 1000 + sk : (wm ? 2000 + wm : (pp ? 3000 + pp : 0)));
     return 0;
 }

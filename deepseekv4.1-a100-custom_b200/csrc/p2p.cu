@@ -103,6 +103,14 @@ int p2p_device_error(int* out) {
 
 int sm_count();
 
+// device addresses of the error word and the wait limit, for kernels of other translation units (per device; looked up every call:
+// cudaGetSymbolAddress is a table look-up once the module is loaded)
+int p2p_words(int** error_word, const unsigned long long** limit_ns) {
+    cudaError_t e = cudaGetSymbolAddress((void**)error_word, g_p2p_error);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress((void**)limit_ns, g_p2p_wait_limit_ns);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 }  // namespace b200
 
 using namespace b200;

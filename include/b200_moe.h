@@ -294,6 +294,47 @@ int b200_p2p_stamp(long long* dst, cudaStream_t stream);
 int b200_memcpy_async(void* dst, const void* src, long long nbytes, cudaStream_t stream);
 int b200_set_wait_limit_ns(unsigned long long ns);
 
+/* ---- expert-parallel decode step over peer memory: the dispatch / return exchange of one MoE layer step among the GPUs of a node as
+ * three stream-ordered kernels with ordinary peer stores and flag words.  Replaces, as ONE protocol, what the reference's decode
+ * runtime assembles from p2p_copy_row / p2p_multicast / p2p_signal / p2p_wait / p2p_sum_rows per layer (dsv41/ep.py:69-80, 356-525).
+ * Every rank owns one slab that all ranks can address; `b200_ep_peers` holds, per rank p, the addresses inside p's slab:
+ *   inbox_x[p]   [tokens][x_row_bytes]       activation rows of all ranks in global token order
+ *   inbox_l[p]   [tokens][l_row_bytes]       router logits rows
+ *   partials[p]  [tokens of p][world][dim]   fp32 partial sums of p's own tokens, one row per contributing rank
+ *   flags_in[p]  address of flags_in[rank] in p's slab;  flags_out[p]  address of flags_out[rank] in p's slab
+ * (all five: DEVICE arrays of `world` addresses), plus local words: first = device int32 [world + 1], first global token of each rank
+ * (first[world] = all tokens); seq = device int32, the step number, starts at 1 with all flags 0; counter = device uint32 [2], zero.
+ * Step on every rank, one stream:  b200_ep_dispatch -> b200_ep_wait(own flags_in, world, seq, 0, 0) -> compute partial fp32 [tokens][dim]
+ * over the rows of the own inbox -> b200_ep_return -> b200_ep_wait(own flags_out, world, seq, 1, 1) -> sum partials[rank] over ranks.
+ * The waits are bounded (b200_set_wait_limit_ns): a wait that gives up stores 3003 (arrival) / 3004 (return) in the device error word
+ * and the step runs on.  Each rank must run on its own GPU (kernels of two ranks that wait for each other cannot share one). */
+#define B200_EP_MAX_RANKS 16
+#define B200_EP_HANDLE_BYTES 64
+typedef struct b200_ep_peers {
+    int rank, world;
+    int dim;                    /* values of a partial row */
+    int x_row_bytes, l_row_bytes; /* multiples of 16 */
+    const int* first;
+    void* const* inbox_x;
+    void* const* inbox_l;
+    int* const* flags_in;
+    float* const* partials;
+    int* const* flags_out;
+    int* seq;
+    unsigned int* counter;
+} b200_ep_peers;
+int b200_ep_dispatch(const b200_ep_peers* peers, const void* x_local, const void* logits_local, int local_tokens, cudaStream_t stream);
+int b200_ep_return(const b200_ep_peers* peers, const float* partial, int tokens, cudaStream_t stream);
+/* waits for flags[0 .. n) >= *seq; advance != 0: then *seq += 1; which: 0 = arrival (code 3003), 1 = return (code 3004) */
+int b200_ep_wait(const int* flags, int n, int* seq, int advance, int which, cudaStream_t stream);
+/* Set-up calls, NOT stream-ordered (they allocate, synchronise the device, map memory): a zero-filled slab of device memory that other
+ * processes may map, its 64-byte handle (CUDA IPC), and the mapping of another process's slab into this one. */
+int b200_ep_alloc(size_t bytes, void** ptr);
+int b200_ep_free(void* ptr);
+int b200_ep_export(const void* ptr, void* handle /* B200_EP_HANDLE_BYTES */);
+int b200_ep_open(const void* handle, void** ptr);
+int b200_ep_close(void* ptr);
+
 /* ---- device error word.  Every device-side wait of this library is bounded; one that runs out of time stores a non-zero
  * code instead of hanging.  Synchronises `stream`, returns the code in *code (0 = none) and clears it. */
 int b200_device_error(int* code, cudaStream_t stream);

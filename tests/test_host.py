@@ -39,6 +39,30 @@ def test_moe_args_struct_matches_header(mods):
     assert names == [f[0] for f in mods.lib.MoeArgs._fields_]
 
 
+def test_ep_peers_struct_matches_header(mods):
+    header = open(os.path.join(ROOT, "include", "b200_moe.h")).read()
+    body = header[header.index("typedef struct b200_ep_peers {"):header.index("} b200_ep_peers;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for stmt in body.split("{", 1)[1].split(";"):
+        stmt = stmt.strip()
+        if stmt:
+            names += [re.sub(r".*[\s\*]", "", n.strip()) for n in stmt.split(",")]
+    assert names == [f[0] for f in mods.lib.EpPeers._fields_]
+    assert f"#define B200_EP_MAX_RANKS {mods.lib.EP_MAX_RANKS}" in header and f"#define B200_EP_HANDLE_BYTES {mods.lib.EP_HANDLE_BYTES}" in header
+
+
+def test_peer_exchange_slab_layout():
+    """Regions of a slab are 256-byte aligned, ordered and disjoint; the flag regions hold the largest supported world."""
+    import __graft_entry__ as g
+    ep, L = g._import("ep"), g._import("_lib")
+    off = ep.PeerExchange.offsets(8, 64, 4096, 8192, 1536)
+    order = ["fin", "fout", "x", "l", "part", "bytes"]
+    assert all(off[k] % 256 == 0 for k in order) and [off[k] for k in order] == sorted(off[k] for k in order)
+    assert off["fout"] - off["fin"] >= 4 * L.EP_MAX_RANKS and off["x"] - off["fout"] >= 4 * L.EP_MAX_RANKS
+    assert off["l"] - off["x"] >= 64 * 8192 and off["part"] - off["l"] >= 64 * 1536 and off["bytes"] - off["part"] >= 64 * 8 * 4096 * 4
+
+
 def test_operators_refuse_cpu_tensors(mods):
     x = torch.zeros(2, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
