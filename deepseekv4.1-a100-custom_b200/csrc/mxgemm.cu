@@ -306,14 +306,15 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                 const MxProb& P = a.p[c.pr];
                 const int4 w = c.w;
                 const uint32_t buf = acc_it % n_acc, aph = (acc_it / n_acc) & 1;
-                const bool ready = mbar_wait(bar_acc_full(buf), aph, &abort_flag, &g_mx_error, 41);
-                tc_fence_after();
-                const int row0 = c.it * rows_w;
-                const bool warp_on = ready && q * 32 < w.z;  // warp-uniform: some token of this warp exists
+                // the row's routing weight and output row are fetched before the wait for the accumulator, not after it
                 const bool tok_on = t < w.z;
                 const int prow = w.y + (tok_on ? t : 0);
                 const float pw = (P.pair_w && tok_on) ? __ldg(P.pair_w + prow) : 1.f;
                 const long orow = (P.pair_out && tok_on) ? (long)__ldg(P.pair_out + prow) : (long)prow;
+                const bool ready = mbar_wait(bar_acc_full(buf), aph, &abort_flag, &g_mx_error, 41);
+                tc_fence_after();
+                const int row0 = c.it * rows_w;
+                const bool warp_on = ready && q * 32 < w.z;  // warp-uniform: some token of this warp exists
                 const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + buf * NW;
                 if (w.z <= a.stg_rows) {
                     // ---- few tokens: a thread per token would leave most lanes idle for the whole epilogue.  The two warps that can
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                             for (int cc = 0; cc < 32; ++cc) {
                                 float gt = __uint_as_float(g[cc]), up = __uint_as_float(u[cc]);
                                 if (P.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
-                                h[cc] = swiglu_bf16(gt, up, pw, a.limit);
+                                h[cc] = swiglu_bf16_fast(gt, up, pw, a.limit);
                                 amax = fmaxf(amax, fabsf(h[cc]));
                             }
                             const float sc = fp8_group_scale_bf16(amax);  // amax is a bf16 value
@@ -393,14 +394,10 @@ __global__ void __launch_bounds__(MX_THREADS, 1) mx_gemm_kernel(const MxArgs a, 
                             const float inv = u32_as_f32((254u - sb) << 23);  // 1 / sc, exact (sc is a power of two)
                             uint32_t o[8];
 #pragma unroll
-                            for (int cc = 0; cc < 8; ++cc) {
-                                uint32_t v = 0;
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const float qv = fminf(fmaxf(h[4 * cc + e] * inv, -448.f), 448.f);
-                                    v |= (uint32_t)__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3) << (8 * e);
-                                }
-                                o[cc] = v;
+                            for (int cc = 0; cc < 8; ++cc) {  // |h / sc| <= 448 by the choice of sc; the conversion saturates anyway
+                                const uint32_t lo2 = __nv_cvt_float2_to_fp8x2(make_float2(h[4 * cc] * inv, h[4 * cc + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                                const uint32_t hi2 = __nv_cvt_float2_to_fp8x2(make_float2(h[4 * cc + 2] * inv, h[4 * cc + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                                o[cc] = lo2 | (hi2 << 16);
                             }
                             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(P.out) + orow * P.out_ld + row0 + c0);
                             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
