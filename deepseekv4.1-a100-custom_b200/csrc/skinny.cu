@@ -149,9 +149,14 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const long wrow_bytes = FP4 ? (K >> 1) : K;
-    const int nst = (int)((wrow_bytes + SK_STAGE_ROW_BYTES - 1) / SK_STAGE_ROW_BYTES);  // stages per item
+    // Narrow items (a.rows32, never with the SwiGLU epilogue): 32 weight rows x 1024 bytes per stage instead of 64 x 512, the 16 warps
+    // are 16 slices of one row half.  Twice as many items for the same matrix: a single GEMV of 4096 rows is 128 items, not 64, for
+    // 148 SMs.
+    const bool r32 = EPI != SK_EPI_SWIGLU && a.rows32 != 0;
+    const int item_rows = r32 ? 32 : SK_ROWS, stage_row_bytes = r32 ? 2 * SK_STAGE_ROW_BYTES : SK_STAGE_ROW_BYTES, n_slices = r32 ? 16 : 8;
+    const int nst = (int)((wrow_bytes + stage_row_bytes - 1) / stage_row_bytes);        // stages per item
     const int n_units = K >> 5;                                                         // activation units per token column
-    const int ipw = (EPI == SK_EPI_SWIGLU) ? (a.inter >> 5) : ((N + SK_ROWS - 1) / SK_ROWS);
+    const int ipw = (EPI == SK_EPI_SWIGLU) ? (a.inter >> 5) : ((N + item_rows - 1) / item_rows);
     // a launch may be tied to a device-side condition (see run_if in skinny.cuh): when it does not hold the kernel has nothing to do
     const bool skip = a.run_if && ((*a.run_if != 0) != (a.run_if_nonzero != 0));
     const int n_work = skip ? 0 : (a.n_work ? *a.n_work : a.n_work_host);
@@ -180,7 +185,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
         const int4 w = get_work(wk);
         d.expert = w.x; d.first = w.y; d.ntok = w.z;
         if (EPI == SK_EPI_SWIGLU) { d.row0a = it * 32; d.row0b = a.inter + it * 32; }
-        else { d.row0a = it * SK_ROWS; d.row0b = it * SK_ROWS + 32; }
+        else { d.row0a = it * item_rows; d.row0b = it * item_rows + 32; }
         return d;
     };
     auto next_desc = [&](const ItemDesc& d) -> ItemDesc {
@@ -204,10 +209,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
                 mbar_expect_tx(full, SK_STAGE_BYTES);
                 const uint32_t dst = smem_u32(ring + (size_t)s * SK_STAGE_BYTES);
 #pragma unroll
-                for (int sl = 0; sl < 4; ++sl) {  // stage layout [row half][128-byte slab][32 rows][128 B]
-                    const int x = st * SK_STAGE_ROW_BYTES + sl * 128;
+                for (int sl = 0; sl < 4; ++sl) {  // stage layout [row half][128-byte slab][32 rows][128 B]; narrow items: [slab 0..7][32 rows][128 B]
+                    const int x = st * stage_row_bytes + sl * 128;
                     tma_load_3d(dst + sl * 4096, &tmap, x, d.row0a, d.expert, full);
-                    tma_load_3d(dst + 16384 + sl * 4096, &tmap, x, d.row0b, d.expert, full);
+                    if (r32) tma_load_3d(dst + 16384 + sl * 4096, &tmap, x + 512, d.row0a, d.expert, full);
+                    else tma_load_3d(dst + 16384 + sl * 4096, &tmap, x, d.row0b, d.expert, full);
                 }
             }
             if (abort_flag) break;
@@ -226,7 +232,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
     }
 
     // ---------------------------------------------------- consumer warps
-    const int rh = warp & 1, kq = warp >> 1;  // row half (32 rows), 64-byte slice of every stage row
+    const int rh = r32 ? 0 : (warp & 1), kq = r32 ? warp : (warp >> 1);  // row half (32 rows), 64-byte slice of every stage row
     ItemDesc d = make_desc(wk_lo, it_lo);
     ItemDesc dn = d;
     auto scale_ptr = [&](const ItemDesc& q, int j) -> const uint8_t* {  // scale row of weight row g + 8 j of this warp's half
@@ -240,7 +246,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
     // row, c = 8 st + kq (one byte or bf16 each).  FP8: k = 512 st + 64 kq + [0, 64) = groups 2 c, 2 c + 1 (E8M0 per 32 k) or the
     // fp32 of block c >> 1 (per 128 k).
     auto load_scales = [&](const ItemDesc& q, int st, uint32_t (&sc)[4], uint32_t (&sc2)[4]) {
-        const int c = st * 8 + kq;
+        const int c = st * n_slices + kq;
         if (c * (FP4 ? 128 : 64) >= K) { sc[0] = sc[1] = sc[2] = sc[3] = 0; sc2[0] = sc2[1] = sc2[2] = sc2[3] = 0; return; }
         if (FMT == SK_FMT_FP4_E8M0) {
 #pragma unroll
@@ -287,7 +293,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
             if (st + 1 < nst) load_scales(d, st + 1, sc_nxt, sc2_nxt);
             else if (has_next) load_scales(dn, 0, sc_nxt, sc2_nxt);
             const bool ready = mbar_wait(smem_u32(&bars[s]), ph, &abort_flag, &g_skinny_error, 2);
-            const int c = st * 8 + kq;
+            const int c = st * n_slices + kq;
             if (ready) {
                 const uint32_t box = smem_u32(ring + (size_t)s * SK_STAGE_BYTES) + lm_row;
                 if (FP4) {
@@ -369,7 +375,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
         // partial sums of the 8 slices -> shared memory (after every warp has finished reading the previous item's sums)
         if (!first_item) consumer_sync();
         first_item = false;
-        float* rp = red + (kq * 64 + rh * 32) * 8;
+        float* rp = red + (kq * item_rows + rh * 32) * 8;  // [slice][row of the item][token column]
         *reinterpret_cast<float2*>(rp + g * 8 + 2 * t) = make_float2(acc[0][0], acc[0][1]);
         *reinterpret_cast<float2*>(rp + (g + 8) * 8 + 2 * t) = make_float2(acc[0][2], acc[0][3]);
         *reinterpret_cast<float2*>(rp + (g + 16) * 8 + 2 * t) = make_float2(acc[1][0], acc[1][1]);
@@ -394,12 +400,17 @@ __global__ void __launch_bounds__(SK_THREADS, 1) skinny_kernel(const SkinnyArgs 
                 reinterpret_cast<__nv_bfloat16*>(a.out)[orow * a.out_ld + it * 32 + lane] = __float2bfloat16_rn(fp8_fake_quant_value(h, s));
             }
         } else {
-            const int col = tid >> 6, rr = tid & 63;
-            const int nrow = it * SK_ROWS + rr;
-            if (col < ntok && nrow < N) {
+            const int col = r32 ? (tid >> 5) : (tid >> 6), rr = r32 ? (tid & 31) : (tid & 63);
+            const int nrow = it * item_rows + rr;
+            if (col < SK_TOK && col < ntok && nrow < N) {
                 float v = 0.f;
+                if (r32) {
 #pragma unroll
-                for (int q = 0; q < 8; ++q) v += red[(q * 64 + rr) * 8 + col];
+                    for (int q = 0; q < 16; ++q) v += red[(q * 32 + rr) * 8 + col];
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) v += red[(q * 64 + rr) * 8 + col];
+                }
                 const int pair = first + col;
                 if (a.pair_w) v *= a.pair_w[pair];
                 const long orow = a.pair_out ? a.pair_out[pair] : pair;
@@ -543,6 +554,14 @@ int skinny_launch(const SkinnyArgs& a_in, int fmt, int epi, cudaStream_t stream)
     a.n_stages = stages;
     const size_t smem = fixed + (size_t)stages * SK_STAGE_BYTES;
     const int grid = sm_count();
+    // 32-row items when they lower the largest share of weight rows a CTA gets (known on the host only when the work count is): a
+    // GEMV of 4096 rows is 64 items of 64 rows for 148 SMs, one of 12288 rows is 192 (two for some CTAs, one for the others)
+    a.rows32 = 0;
+    if (epi != SK_EPI_SWIGLU && !a.n_work) {
+        const long works = a.work ? a.n_work_host : (a.dense_rows + SK_TOK - 1) / SK_TOK;
+        const long i64 = works * ((a.N + 63) / 64), i32 = works * ((a.N + 31) / 32);
+        if ((i32 + grid - 1) / grid < 2 * ((i64 + grid - 1) / grid)) a.rows32 = 1;
+    }
     const bool fp4 = fmt == SK_FMT_FP4_E8M0 || fmt == SK_FMT_FP4_BF16S;
     const uint64_t row_bytes = fp4 ? (uint64_t)a.K / 2 : (uint64_t)a.K;
     alignas(64) CUtensorMap tm;

@@ -47,6 +47,7 @@ struct SkinnyArgs {
     int inter;              // N == 2*inter for SK_EPI_SWIGLU
     int round_gu_bf16;      // round gate/up to bf16 before SwiGLU (shared expert)
     int n_stages;           // ring depth, set by skinny_launch from the shared-memory budget
+    int rows32;             // items of 32 weight rows instead of 64 (set by skinny_launch when 64-row items would leave SMs without work)
     const int* run_if;      // optional device word: the launch does its work only if (*run_if != 0) == (run_if_nonzero != 0)
     int run_if_nonzero;
 };
