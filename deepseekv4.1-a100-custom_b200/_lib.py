@@ -30,7 +30,7 @@ class MoeArgs(ctypes.Structure):
                 ("shared_fmt", c_i), ("sh_s13_cols", c_i), ("sh_s2_cols", c_i), ("sh_permk", c_i), ("swiglu_limit", c_f),
                 ("out", c_p), ("routed_out", c_p), ("eid_out", c_p), ("wt_out", c_p), ("workspace", c_p), ("workspace_bytes", c_sz),
                 ("prof_start", c_p), ("prof_stop", c_p), ("engine", c_i), ("shared_out", c_p), ("x_ld", c_ll), ("logits_ld", c_ll), ("gate_w", c_p), ("xf", c_p), ("xf_ld", c_ll),
-                ("s13_atoms", c_p), ("s2_atoms", c_p), ("sh_s13_atoms", c_p), ("sh_s2_atoms", c_p), ("eid_in", c_p), ("wt_in", c_p)]
+                ("s13_atoms", c_p), ("s2_atoms", c_p), ("sh_s13_atoms", c_p), ("sh_s2_atoms", c_p), ("eid_in", c_p), ("wt_in", c_p), ("sh_first", c_i), ("sh_count", c_i)]
 
 
 class EpPeers(ctypes.Structure):

@@ -659,6 +659,7 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (m->eid_in && (!m->wt_in || m->tokens > DQ_MAX_TOKENS || !m->s13_atoms)) return ERR_UNSUPPORTED;  // given routing: decode-sized batches only
     if ((!m->logits && !m->gate_w && !m->eid_in) || !m->x || !m->w13 || !m->s13 || !m->w2 || !m->s2 || !m->workspace) return ERR_BAD_ARG;
     if (m->has_shared && (!m->sh_w13 || !m->sh_s13 || !m->sh_w2 || !m->sh_s2)) return ERR_BAD_ARG;
+    if (m->sh_count < 0 || m->sh_first < 0 || (m->sh_count > 0 && (m->out || m->sh_first + m->sh_count > m->tokens))) return ERR_BAD_ARG;
     const int T = m->tokens, topk = m->topk, D = m->dim, I = m->inter, E = m->n_experts;
     const long P = (long)T * topk;
     if (P > (1L << 30) || E > ROUTE_MAX_EXPERTS || topk > 32 || topk > E) return ERR_BAD_SHAPE;
@@ -820,6 +821,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
         // always the widest tiles (256 weight rows per MMA): even when that leaves fewer (work, tile) items than SMs, as for a single
         // token (6 works x 16 tiles), the wide tiles stream faster than more, narrower ones (measured 83 us against 136 us per step)
         const int rows1 = 128, rows2 = 256;
+        // the shared expert's rows: all tokens, or the sub-range the caller keeps
+        const int sh_first = m->sh_count > 0 ? m->sh_first : 0, sh_rows = m->sh_count > 0 ? m->sh_count : T;
         // each GEMM launch carries the routed experts (problem 0) and, behind them in the same item list, the shared expert
         // (problem 1: one FP8 matrix against all tokens)
         MxArgs g1{};
@@ -837,9 +840,9 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             MxProb& q = g1.p[1];
             q.w = m->sh_w13; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
             q.s = (const uint8_t*)m->sh_s13; q.s_rstride = m->sh_s13_cols; q.s_row_shift = 5;
-            q.N = 2 * I; q.x8 = w.x8t; q.x8_rows = T + 128; q.xsf = w.xsft; q.xsf_ld = D / 32;
-            q.work = nullptr; q.dense_rows = T; q.n_work_host = (T + nd - 1) / nd; q.epi = MX_EPI_SWIGLU_Q8;
-            q.out = w.hs8; q.out_ld = I; q.out_sf = w.hssf; q.out_sf_ld = I / 32; q.round_gu_bf16 = 1;
+            q.N = 2 * I; q.x8 = w.x8t + (size_t)sh_first * D; q.x8_rows = T + 128 - sh_first; q.xsf = w.xsft + (size_t)sh_first * (D / 32); q.xsf_ld = D / 32;
+            q.work = nullptr; q.dense_rows = sh_rows; q.n_work_host = (sh_rows + nd - 1) / nd; q.epi = MX_EPI_SWIGLU_Q8;
+            q.out = w.hs8; q.out_ld = I; q.out_sf = w.hssf; q.out_sf_ld = I / 32; q.round_gu_bf16 = 1;  // rows 0 .. sh_rows-1 of hs8
         }
         if (m->prof_start && (ce = cudaEventRecord((cudaEvent_t)m->prof_start, stream)) != cudaSuccess) return (int)ce;
         if ((rc = mx_launch(g1, stream))) return rc;
@@ -861,8 +864,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             q.w = m->sh_w2; q.n_experts = 1; q.a_fmt = MX_A_E4M3;
             q.s = (const uint8_t*)m->sh_s2; q.s_rstride = m->sh_s2_cols; q.s_row_shift = 5;
             q.N = D; q.x8 = w.hs8; q.x8_rows = T + 128; q.xsf = w.hssf; q.xsf_ld = I / 32;
-            q.work = nullptr; q.dense_rows = T; q.n_work_host = (T + nd - 1) / nd; q.epi = MX_EPI_STORE_BF16;
-            q.out = ys_buf; q.out_ld = D;
+            q.work = nullptr; q.dense_rows = sh_rows; q.n_work_host = (sh_rows + nd - 1) / nd; q.epi = MX_EPI_STORE_BF16;
+            q.out = ys_buf + (size_t)sh_first * D; q.out_ld = D;
         }
         if ((rc = mx_launch(g2, stream))) return rc;
     } else {

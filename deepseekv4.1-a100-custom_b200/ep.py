@@ -319,12 +319,13 @@ class EPMoE:
             mark(1)
             x_all = b["both"][:, :xb].view(x_local.dtype)
             l_all = b["both"][:, xb:].view(logits_local.dtype)
-            # local experts over all tokens; the shared expert rides in the same launches, this rank keeps its own rows of the result
+            # local experts over all tokens; the shared expert rides in the same launches, for this rank's own token rows only
             has_sh = self.layer.sh_w13 is not None
-            self.layer.forward(x_all, l_all, final=False, want_routed=True, routed_out=b["part"], want_shared=has_sh, shared_out=b["ys"] if has_sh else None)
+            first = sum(counts[:self.rank])
+            self.layer.forward(x_all, l_all, final=False, want_routed=True, routed_out=b["part"], want_shared=has_sh, shared_out=b["ys"] if has_sh else None,
+                               shared_rows=(first, T_r) if has_sh else None)
             mark(2)
             dist.reduce_scatter_tensor(b["routed"], b["part"], group=self.group)
-            first = sum(counts[:self.rank])
             res = moe_combine(b["routed"].unsqueeze(1), b["ys"][first:first + T_r] if has_sh else None, out=out)
             mark(3)
             return res

@@ -114,14 +114,16 @@ class MoELayer:
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor | None = None, *, xf: torch.Tensor | None = None, out: torch.Tensor | None = None, want_routed: bool = False, want_route: bool = False,
                 x_is_quantized: bool = False, with_shared: bool = True, final: bool = True, want_shared: bool = False, prof_events=None,
-                eid: torch.Tensor | None = None, wt: torch.Tensor | None = None, shared_out: torch.Tensor | None = None, routed_out: torch.Tensor | None = None):
+                eid: torch.Tensor | None = None, wt: torch.Tensor | None = None, shared_out: torch.Tensor | None = None, routed_out: torch.Tensor | None = None,
+                shared_rows: tuple[int, int] | None = None):
         """x bf16 [T, D] (the hidden state before the per-32 FP8 fake quantisation), logits fp32|bf16 [T, E]; logits=None (the layer was
         built with gate_w): the router projection xf @ gate_w^T runs inside the call, xf fp32 [T, D] or None for x.float()
         (dsv41/decode.py:449, dsv41/model.py:1615).
         eid int32 / wt fp32 [T, topk]: routing decided by the caller instead of logits (at most 64 tokens, E8M0 formats).
         Returns out bf16 [T, D] = routed experts of this shard + shared expert; optionally also the fp32 routed partial sum
         and (eid, wt).  prof_events: a pair of torch.cuda.Event recorded around the routed gate/up kernel.  shared_out / routed_out:
-        caller-provided buffers for the shared expert's result (bf16) and the routed sum (fp32) instead of fresh ones."""
+        caller-provided buffers for the shared expert's result (bf16) and the routed sum (fp32) instead of fresh ones.  shared_rows =
+        (first, count): the caller keeps only these rows of the shared expert's result (final=False), the others are unspecified."""
         dev = L.require_cuda(x, logits, out)
         # rows may be strided (views into a wider buffer), the elements of a row are contiguous
         assert dev == self.device and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.dim and x.stride(1) == 1
@@ -187,6 +189,10 @@ class MoELayer:
         a.eid_out = eid_o.data_ptr() if eid_o is not None else None
         a.wt_out = wt_o.data_ptr() if wt_o is not None else None
         a.eid_in, a.wt_in = (eid.data_ptr(), wt.data_ptr()) if given else (None, None)
+        a.sh_first, a.sh_count = (0, 0)
+        if shared_rows is not None:
+            assert not final and 0 <= shared_rows[0] and shared_rows[0] + shared_rows[1] <= T
+            a.sh_first, a.sh_count = int(shared_rows[0]), int(shared_rows[1])
         if prof_events is not None:  # (start, stop) torch.cuda.Event pair, already created (recorded once), timing enabled
             a.prof_start, a.prof_stop = prof_events[0].cuda_event, prof_events[1].cuda_event
         else:

@@ -221,6 +221,11 @@ typedef struct b200_moe_args {
      * dsv41/cukern.py:504-547): no router runs and `logits` may be NULL.  Needs the scale atoms above and at most 64 tokens. */
     const int* eid_in;
     const float* wt_in;
+    /* optional: the shared expert for the token rows [sh_first, sh_first + sh_count) only (sh_count = 0: all tokens).  For callers that
+     * keep only those rows of shared_out, as a rank of an expert-parallel group keeps its own tokens: in a prefill-sized call the shared
+     * expert otherwise costs as much as all routed pairs of the rank together.  Needs out == NULL; rows of shared_out outside the range
+     * are unspecified (calls that stream the shared expert's weights once for all tokens compute every row regardless). */
+    int sh_first, sh_count;
 } b200_moe_args;
 
 size_t b200_moe_workspace_bytes(int tokens, int topk, int dim, int inter);

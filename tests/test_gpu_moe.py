@@ -127,6 +127,24 @@ def test_shared_expert_as_separate_output(mods, dev, T, engine):
     assert mods.cukern.device_error(dev) == 0
 
 
+@pytest.mark.parametrize("T,rows", [(300, (128, 75)), (900, (700, 200)), (900, (0, 900)), (40, (8, 8))])
+def test_shared_expert_for_a_row_range_only(mods, dev, T, rows):
+    # a rank of an expert-parallel group keeps its own token rows of the shared expert's result: those rows are the bits of the
+    # full call, the routed sums are untouched
+    E, D, I, topk = 16, 512, 256, 4
+    _, _, layer = _layer(mods, dev, E, D, I, topk, 31)
+    x = mods.synth.make_tokens(T, D, 35).to(dev)
+    logits = mods.synth.make_logits(T, E, 36, topk=topk).to(dev)
+    routed, ys = layer.forward(x, logits, final=False, want_routed=True, want_shared=True)
+    ys2 = torch.full_like(ys, float("nan"))
+    routed2 = layer.forward(x, logits, final=False, want_routed=True, want_shared=True, shared_out=ys2, shared_rows=rows)[0]
+    a, n = rows
+    assert torch.equal(ys2[a:a + n], ys[a:a + n]) and rel_err(routed2, routed) < 1e-5  # (the large batch adds with atomics)
+    assert mods.cukern.device_error(dev) == 0
+    with pytest.raises(AssertionError):
+        layer.forward(x, logits, shared_rows=rows)  # only for calls that do not form the final output
+
+
 def test_expert_parallel_layer_world_of_one_equals_layer(mods, dev):
     # the CUDA defaults of the expert-parallel wrapper (shared expert fused into the local launches) on a one-rank group
     import os
