@@ -182,6 +182,35 @@ __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const RouteArg
     }
 }
 
+// Router alone for prefill-sized batches whose pairs are bucketed by the multi-block kernels below: one WARP per token, eight tokens per
+// block, scratch of 3 E floats per warp.  (moe_route_kernel keeps 50 KB of bucketing tables per block, which leaves four one-warp
+// routers per SM: 70 us for 4096 tokens.)
+constexpr int ROUTE_ROWS_PER_BLOCK = 8;
+__global__ void __launch_bounds__(32 * ROUTE_ROWS_PER_BLOCK) route_rows_kernel(const RouteArgs a) {
+    extern __shared__ float route_smem[];  // per warp: E scores, E keys, E raw logits
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long tok = (long)blockIdx.x * ROUTE_ROWS_PER_BLOCK + warp;
+    if (tok >= a.tokens) return;
+    float* s_val = route_smem + (size_t)warp * 3 * a.E;
+    float* s_key = s_val + a.E;
+    float* s_raw = s_key + a.E;
+    const float* row_f32 = a.logits_f32 ? a.logits_f32 + tok * a.logits_ld : nullptr;
+    if (a.logit_parts > 0) {  // k-split partial sums of the fused router projection, added in split order
+        const float* base = a.logits_f32 + tok * a.E;
+        for (int e = lane; e < a.E; e += 32) {
+            float v = 0.f;
+#pragma unroll 4
+            for (int p = 0; p < a.logit_parts; ++p) v += __ldg(base + (long long)p * a.logit_part_stride + e);
+            s_raw[e] = v;
+        }
+        __syncwarp();
+        row_f32 = s_raw;
+    }
+    gate_topk_warp(row_f32, a.logits_bf16 ? a.logits_bf16 + tok * a.logits_ld : nullptr, a.bias, a.E, a.temp, a.topk, a.route_scale, a.mode, a.norm,
+                   a.eid + tok * a.topk, a.wt + tok * a.topk, s_val, s_key);
+}
+
 // ------------------------------------------------------------------ decode-sized batches (at most 64 tokens) on the weight-stream kernels
 // One block per token: FP8 quantisation of the token's activation kept in quantised form (e4m3 bytes + the E8M0 scale bytes written
 // straight into the 512-byte atoms the tensor cores read, see wmgemm.cu), and the router.  The last block to finish lists the
@@ -456,6 +485,21 @@ __global__ void moe_finalize_kernel(const float* __restrict__ acc, const __nv_bf
     pdl_wait();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2bfloat16_rn(acc[i] + (ys ? __bfloat162float(ys[i]) : 0.f));
+}
+// the same, eight values per thread with 16-byte accesses (all three pointers 16-byte aligned, n a multiple of 8)
+__global__ void moe_finalize_vec_kernel(const float4* __restrict__ acc, const uint4* __restrict__ ys, uint4* __restrict__ out, long n8) {
+    pdl_wait();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const float4 a0 = acc[2 * i], a1 = acc[2 * i + 1];
+    const uint4 y = ys ? ys[i] : make_uint4(0, 0, 0, 0);
+    const float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t yw[4] = {y.x, y.y, y.z, y.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        o[j] = f32_to_bf16_bits(f[2 * j] + bf16_bits_to_f32(yw[j] & 0xFFFFu)) | (f32_to_bf16_bits(f[2 * j + 1] + bf16_bits_to_f32(yw[j] >> 16)) << 16);
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // out[t, n] = bf16( sum over the token's LOCAL experts of y2[t*topk + j, n] + float(ys[t, n]) )  (dsv41/fused2.py:518-523);
@@ -801,7 +845,11 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     if (small) {  // the counter of the "last block" election starts at zero and resets itself after every launch
         if ((ce = cudaMemsetAsync(w.counter, 0, sizeof(unsigned int), stream)) != cudaSuccess) return (int)ce;
     }
-    moe_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
+    if (r.no_bucket && !r.xq && (size_t)ROUTE_ROWS_PER_BLOCK * 3 * E * sizeof(float) <= 48 * 1024) {
+        route_rows_kernel<<<(T + ROUTE_ROWS_PER_BLOCK - 1) / ROUTE_ROWS_PER_BLOCK, 32 * ROUTE_ROWS_PER_BLOCK, (size_t)ROUTE_ROWS_PER_BLOCK * 3 * E * sizeof(float), stream>>>(r);
+    } else {
+        moe_route_kernel<<<T, ROUTE_THREADS, 0, stream>>>(r);
+    }
     B200_CHECK_LAUNCH();
     if (!small) {  // many pairs: multi-block histogram / scan / scatter; GEMM-2 adds into a per-token accumulator
         if ((ce = cudaMemsetAsync(w.cnt, 0, sizeof(int) * ROUTE_MAX_EXPERTS, stream)) != cudaSuccess) return (int)ce;
@@ -917,8 +965,13 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             return (int)ce;
     } else {
         if (m->out) {
-            if ((ce = launch_pdl(moe_finalize_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.acc,
-                                 (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, n)) != cudaSuccess)
+            const __nv_bfloat16* ysp = shared ? ys_buf : nullptr;
+            if (n % 8 == 0 && !(((uintptr_t)w.acc | (uintptr_t)ysp | (uintptr_t)m->out) & 15)) {
+                if ((ce = launch_pdl(moe_finalize_vec_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, stream, (const float4*)w.acc, (const uint4*)ysp,
+                                     (uint4*)m->out, n / 8)) != cudaSuccess)
+                    return (int)ce;
+            } else if ((ce = launch_pdl(moe_finalize_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.acc, ysp,
+                                        (__nv_bfloat16*)m->out, n)) != cudaSuccess)
                 return (int)ce;
         }
         if (m->routed_out && (ce = cudaMemcpyAsync(m->routed_out, w.acc, sizeof(float) * n, cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
