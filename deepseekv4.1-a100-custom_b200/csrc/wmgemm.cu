@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
     __shared__ uint8_t s_slot[WM_NT_MAX];    // the current work's table over the tokens
     __shared__ int s_live[WM_NT_MAX + 1];    // tokens that take part, then their count at [WM_NT_MAX]
     __shared__ int s_pos[WM_NT_MAX];         // index of a token among the taking-part ones (-1: it does not)
+    __shared__ uint8_t s_pred[WM_MAX_PRED];  // CTAs that hold earlier k blocks of the tile being finished (as distances back from this CTA), and their number
+    __shared__ int s_npred;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int NS = a.n_stages, NT = a.NT, KBLK = a.K >> 7;
@@ -103,9 +105,45 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
     const long tiles = tiles0 + tiles1;
     const long U = tiles * KBLK;
     const long G = gridDim.x;
-    auto unit_lo = [&](long c) -> long { return a.split_k ? U * c / G : (tiles * c / G) * KBLK; };
-    const long lo = unit_lo(blockIdx.x), hi = unit_lo(blockIdx.x + 1);
     const long gap = tiles1 > 0 ? tiles / tiles1 : 1;
+    // The cut is even in BYTES, not in k blocks: a k block of an FP8 matrix (the shared expert) is twice the bytes of a packed FP4 one.
+    // cost_at(u) = weight of the k blocks before u; CTA c starts at the first u whose cost reaches c / G of the total.
+    // (measured: a k block of an FP8 matrix takes about 1.5 times as long as a packed FP4 one, not twice: weights 3 and 2)
+    const int wc0 = a.p[0].a_fmt == MX_A_E2M1 ? 2 : 3, wc1 = (a.n_prob > 1 && a.p[1].a_fmt != MX_A_E2M1) ? 3 : 2;
+    // 32-bit arithmetic throughout (at most 384 works x 16 tiles x 80 k blocks x 2 x 192 CTAs < 2^31): these run on the critical path
+    const int gap_i = (int)gap, t1_i = (int)tiles1, tile_c0 = wc0 * KBLK, tile_c1 = wc1 * KBLK;
+    const int period_c = (gap_i - 1) * tile_c0 + tile_c1;      // cost of `gap` consecutive tiles while problem 1 has tiles left
+    const int cost_all = (int)(tiles0 * tile_c0 + tiles1 * tile_c1);
+    auto cost_at = [&](long u) -> int {
+        const int ui = (int)u, tile = ui / KBLK, within = ui - tile * KBLK;
+        const int nb = t1_i > 0 ? (tile / gap_i < t1_i ? tile / gap_i : t1_i) : 0;
+        const bool is1 = t1_i > 0 && tile % gap_i == gap_i - 1 && tile / gap_i < t1_i;
+        return (tile - nb) * tile_c0 + nb * tile_c1 + within * (is1 ? wc1 : wc0);
+    };
+    auto unit_lo = [&](long c) -> long {  // the first unit whose preceding cost reaches c / G of the total (closed form of the inverse of cost_at)
+        if (!a.split_k) return (tiles * c / G) * KBLK;
+        if (c <= 0) return 0;
+        if (c >= G) return U;
+        const int x = (int)((long)cost_all * c / G);
+        int tile, rem, w;
+        if (t1_i > 0 && x < t1_i * period_c) {
+            const int j = x / period_c, r = x - j * period_c;
+            if (r < (gap_i - 1) * tile_c0) { const int q = r / tile_c0; tile = j * gap_i + q; rem = r - q * tile_c0; w = wc0; }
+            else { tile = j * gap_i + gap_i - 1; rem = r - (gap_i - 1) * tile_c0; w = wc1; }
+        } else {
+            const int y = x - t1_i * period_c, q = y / tile_c0;
+            tile = t1_i * gap_i + q; rem = y - q * tile_c0; w = wc0;
+        }
+        return (long)tile * KBLK + (rem + w - 1) / w;
+    };
+    const long lo = unit_lo(blockIdx.x), hi = unit_lo(blockIdx.x + 1);
+    const int nwork0 = (int)(tiles0 / tpw0) > 0 ? (int)(tiles0 / tpw0) : 1, nwork1 = (int)(tiles1 / tpw1) > 0 ? (int)(tiles1 / tpw1) : 1;
+    int wstride0 = (int)(nwork0 * 0.618f) | 1;  // near the golden ratio of the list, then the next value coprime to its length
+    for (;; ++wstride0) {
+        int x = wstride0, y = nwork0;
+        while (y) { const int t = x % y; x = y; y = t; }
+        if (x == 1) break;
+    }
 
     struct Seg { long tile; int kb0, kb1, pr, wk, it, e; };
     auto seg_at = [&](long u) -> Seg {
@@ -118,24 +156,47 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
         // every `gap - 1` tiles of problem 0, so that no CTA gets more than its share of them
         const long nb = s.tile / gap < tiles1 ? s.tile / gap : tiles1;   // tiles of problem 1 before this position
         s.pr = (tiles1 > 0 && s.tile % gap == gap - 1 && s.tile / gap < tiles1) ? 1 : 0;
-        const long rel = s.pr ? nb : s.tile - nb;
-        const int tpw = s.pr ? tpw1 : tpw0;
-        s.wk = (int)(rel / tpw);
-        s.it = (int)(rel - (long)s.wk * tpw);
+        // Order of a problem's tiles: tile index major, works minor, the works taken with a stride coprime to their number.  Tiles of
+        // an expert that many tokens chose cost more (more accumulator rows to move out); consecutive positions of the sequence then
+        // belong to experts far apart in the work list, so every CTA's share is a mix.
+        const int rel = (int)(s.pr ? nb : s.tile - nb);
+        const int nw = s.pr ? nwork1 : nwork0;
+        s.it = rel / nw;
+        const int j = rel - s.it * nw;
+        s.wk = s.pr ? j : (int)(((long)j * wstride0) % nw);
         s.e = a.p[s.pr].work ? __ldg(a.p[s.pr].work + s.wk) : 0;
         return s;
     };
     // Order of this CTA's segments: a CTA that ends inside a tile computes that trailing share FIRST and publishes it at once, then
     // walks the rest of its range in order.  The CTA that finishes the tile needs the share for its first epilogue, about as many
     // k blocks later; published at the end of the range instead, every CTA would wait for the whole range of the one before it.
-    const bool tail_first = a.split_k && (hi % KBLK != 0) && ((hi / KBLK) * KBLK > lo);
-    const long u_tail = tail_first ? (hi / KBLK) * KBLK : hi;
-    struct It { long u; bool tail, done; };
-    auto it_begin = [&]() -> It { return tail_first ? It{u_tail, true, false} : It{lo, false, lo >= u_tail}; };
+    // ... and a CTA that begins inside a tile and finishes it (it then adds the shares of the CTAs before it) computes that leading
+    // part LAST: one of those CTAs may lie inside the tile with its whole range and publish only at its end, and a leading part done
+    // first would wait for it with the accumulator in hand.  Order: trailing share, whole tiles, leading part.
+    const bool has_head = a.split_k && (lo % KBLK != 0) && ((lo / KBLK + 1) * KBLK <= hi);
+    const long head_end = has_head ? (lo / KBLK + 1) * KBLK : lo;  // leading part = [lo, head_end)
+    const long tail_floor = (hi / KBLK) * KBLK;
+    const long tail_start = (a.split_k && hi % KBLK != 0) ? (tail_floor > head_end ? tail_floor : head_end) : hi;  // trailing share = [tail_start, hi)
+    struct It { long u; int ph; bool done; };
+    auto it_enter = [&](It& it, int ph) {  // the first non-empty part from `ph` on
+        for (; ph < 3; ++ph) {
+            if (ph == 0 && tail_start < hi) { it = It{tail_start, 0, false}; return; }
+            if (ph == 1 && head_end < tail_start) { it = It{head_end, 1, false}; return; }
+            if (ph == 2 && lo < head_end) { it = It{lo, 2, false}; return; }
+        }
+        it = It{hi, 3, true};
+    };
+    auto it_begin = [&]() -> It {
+        It it;
+        it_enter(it, 0);
+        return it;
+    };
     auto it_next = [&](It& it, const Seg& sg) {
-        if (it.tail) { it.tail = false; it.u = lo; }
-        else it.u = sg.tile * KBLK + sg.kb1;
-        it.done = it.u >= u_tail;
+        if (it.ph == 1) {
+            const long u = sg.tile * KBLK + sg.kb1;
+            if (u < tail_start) { it.u = u; return; }
+        }
+        it_enter(it, it.ph + 1);
     };
 
     if (lo < hi) {
@@ -240,14 +301,30 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                     s_pos[lane + 32] = l1 ? p1i : -1;
                     if (lane == 0) s_live[WM_NT_MAX] = __popc(m0) + __popc(m1);
                 }
-                long c_first = blockIdx.x;
-                if (owner && sg.kb0 > 0) {  // CTAs c_first .. blockIdx.x - 1 hold the k blocks [0, kb0) of this tile
-                    const long u0 = sg.tile * KBLK;
-                    c_first = u0 * G / U;
-                    while (c_first + 1 < G && unit_lo(c_first + 1) <= u0) ++c_first;
-                    while (c_first > 0 && unit_lo(c_first) > u0) --c_first;
-                    for (long c = c_first; c < (long)blockIdx.x; ++c) {
-                        if (unit_lo(c) == unit_lo(c + 1)) continue;  // a CTA without work leaves nothing
+                // the CTAs that hold the k blocks [0, kb0) of this tile, in CTA order (one thread finds them, all wait for their shares)
+                if (et == 0) {
+                    int np = 0;
+                    if (owner && sg.kb0 > 0) {
+                        const long u0 = sg.tile * KBLK;
+                        long c_first = (long)cost_at(u0) * G / cost_all;
+                        if (c_first >= (long)blockIdx.x) c_first = (long)blockIdx.x - 1;
+                        if (c_first < 0) c_first = 0;
+                        while (c_first + 1 < (long)blockIdx.x && unit_lo(c_first + 1) <= u0) ++c_first;
+                        while (c_first > 0 && unit_lo(c_first) > u0) --c_first;
+                        long ulo = unit_lo(c_first);
+                        for (long c = c_first; c < (long)blockIdx.x && np < WM_MAX_PRED; ++c) {
+                            const long unext = unit_lo(c + 1);
+                            if (unext != ulo) s_pred[np++] = (uint8_t)((long)blockIdx.x - c);  // a CTA without work leaves nothing
+                            ulo = unext;
+                        }
+                    }
+                    s_npred = np;
+                }
+                wm_epi_bar();
+                const int n_pred = s_npred;
+                {
+                    for (int pi = 0; pi < n_pred; ++pi) {
+                        const int c = (int)blockIdx.x - s_pred[pi];
                         unsigned long long ts = 0;
                         for (uint32_t i = 0; !abort_flag && ld_acquire(a.flags + c) != a.flag_value; ++i) {
                             __nanosleep(64);
@@ -310,9 +387,8 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                             const int r = task >> 2, g = task & 3, t = s_live[p0 + r], col = row0 + g * 32 + lane;
                             if (row0 + g * 32 >= a.inter) continue;
                             float gt = stg[(size_t)r * WM_STG_LD + g * 32 + lane], up = stg[(size_t)r * WM_STG_LD + 128 + g * 32 + lane];
-                            for (long cc = c_first; cc < (long)blockIdx.x; ++cc) {
-                                if (unit_lo(cc) == unit_lo(cc + 1)) continue;
-                                const float* src = a.partial + ((size_t)cc * WM_NT_MAX + t) * WM_TILE_ROWS + g * 32 + lane;
+                            for (int pi = 0; pi < n_pred; ++pi) {
+                                const float* src = a.partial + ((size_t)(blockIdx.x - s_pred[pi]) * WM_NT_MAX + t) * WM_TILE_ROWS + g * 32 + lane;
                                 gt += __ldcg(src);
                                 up += __ldcg(src + 128);
                             }
@@ -339,9 +415,8 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                                 *reinterpret_cast<float4*>(a.partial + ((size_t)blockIdx.x * WM_NT_MAX + t) * WM_TILE_ROWS + h * 128 + c) = v;
                                 continue;
                             }
-                            for (long cc = c_first; cc < (long)blockIdx.x; ++cc) {  // the shares of the CTAs before this one, in CTA order
-                                if (unit_lo(cc) == unit_lo(cc + 1)) continue;
-                                const float4 p4 = __ldcg(reinterpret_cast<const float4*>(a.partial + ((size_t)cc * WM_NT_MAX + t) * WM_TILE_ROWS + h * 128 + c));
+                            for (int pi = 0; pi < n_pred; ++pi) {  // the shares of the CTAs before this one, in CTA order
+                                const float4 p4 = __ldcg(reinterpret_cast<const float4*>(a.partial + ((size_t)(blockIdx.x - s_pred[pi]) * WM_NT_MAX + t) * WM_TILE_ROWS + h * 128 + c));
                                 v.x += p4.x; v.y += p4.y; v.z += p4.z; v.w += p4.w;
                             }
                             if (c >= ok_h[h]) continue;
@@ -467,7 +542,7 @@ static int wm_prob_tmaps(const WmArgs& a, const WmProb& p, CUtensorMap* tm_w, CU
 int wm_launch(const WmArgs& a_in, cudaStream_t stream) {
     WmArgs a = a_in;
     if (a.n_prob < 1 || a.n_prob > 2) return ERR_BAD_ARG;
-    if (a.K <= 0 || a.K % 128) return ERR_BAD_SHAPE;
+    if (a.K <= 0 || a.K % 128 || a.K / 128 > WM_MAX_PRED) return ERR_BAD_SHAPE;
     if (a.NT != 16 && a.NT != 32 && a.NT != 64) return ERR_BAD_SHAPE;
     if (a.dual && (a.inter <= 0 || a.inter % 32)) return ERR_BAD_SHAPE;
     if (a.split_k && (!a.partial || !a.flags)) return ERR_BAD_ARG;

@@ -13,6 +13,7 @@ constexpr int WM_NT_MAX = 64;        // token columns of a tile
 constexpr int WM_TILE_ROWS = 256;    // weight rows of a tile = N of the MMA: two blocks of 128 (gate | up, or consecutive)
 constexpr int WM_SF_COL0 = 256;      // TMEM: the scale columns follow the accumulator (128 lanes x 256 columns)
 constexpr int WM_EPI_WARPS = 8;
+constexpr int WM_MAX_PRED = 80;      // CTAs whose shares of one tile a finishing CTA adds: each holds at least one of the tile's k blocks (K <= 10240)
 constexpr int WM_STG_ROWS = 32;      // token rows of the staging buffer (tiles with more taking-part tokens take two passes)
 constexpr int WM_STG_LD = 260;       // its row stride in floats: 16-byte aligned rows, conflict-free for 16-byte row writes and reads
 constexpr size_t WM_PARTIAL_BYTES = (size_t)WM_NT_MAX * WM_TILE_ROWS * sizeof(float);  // one CTA's partial tile: [token][column]
