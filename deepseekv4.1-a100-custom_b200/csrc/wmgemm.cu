@@ -96,35 +96,35 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
     pdl_wait();
     pdl_launch_dependents();
 
+    // (all unit arithmetic in 32 bits: 64-bit divisions on the lone threads that walk the sequence cost microseconds per launch)
     // ---- the flat sequence of k blocks: tiles of problem 0 (work-major) with those of problem 1 spread evenly among them; this CTA
     // owns units [lo, hi)
     const int tpw0 = a.dual ? (a.inter + 127) >> 7 : (a.p[0].N + WM_TILE_ROWS - 1) / WM_TILE_ROWS;
     const int tpw1 = a.n_prob > 1 ? (a.dual ? (a.inter + 127) >> 7 : (a.p[1].N + WM_TILE_ROWS - 1) / WM_TILE_ROWS) : 1;
-    const long tiles0 = (long)(a.p[0].n_work ? *a.p[0].n_work : a.p[0].n_work_host) * tpw0;
-    const long tiles1 = a.n_prob > 1 ? (long)(a.p[1].n_work ? *a.p[1].n_work : a.p[1].n_work_host) * tpw1 : 0;
-    const long tiles = tiles0 + tiles1;
-    const long U = tiles * KBLK;
-    const long G = gridDim.x;
-    const long gap = tiles1 > 0 ? tiles / tiles1 : 1;
-    // The cut is even in BYTES, not in k blocks: a k block of an FP8 matrix (the shared expert) is twice the bytes of a packed FP4 one.
+    const int tiles0 = (a.p[0].n_work ? *a.p[0].n_work : a.p[0].n_work_host) * tpw0;
+    const int tiles1 = a.n_prob > 1 ? (a.p[1].n_work ? *a.p[1].n_work : a.p[1].n_work_host) * tpw1 : 0;
+    const int tiles = tiles0 + tiles1;
+    const int U = tiles * KBLK;
+    const int G = gridDim.x;
+    const int gap = tiles1 > 0 ? tiles / tiles1 : 1;
+    // The cut is even in TIME, not in k blocks: a k block of an FP8 matrix (the shared expert) is twice the bytes of a packed FP4 one.
     // cost_at(u) = weight of the k blocks before u; CTA c starts at the first u whose cost reaches c / G of the total.
     // (measured: a k block of an FP8 matrix takes about 1.5 times as long as a packed FP4 one, not twice: weights 3 and 2)
     const int wc0 = a.p[0].a_fmt == MX_A_E2M1 ? 2 : 3, wc1 = (a.n_prob > 1 && a.p[1].a_fmt != MX_A_E2M1) ? 3 : 2;
-    // 32-bit arithmetic throughout (at most 384 works x 16 tiles x 80 k blocks x 2 x 192 CTAs < 2^31): these run on the critical path
     const int gap_i = (int)gap, t1_i = (int)tiles1, tile_c0 = wc0 * KBLK, tile_c1 = wc1 * KBLK;
     const int period_c = (gap_i - 1) * tile_c0 + tile_c1;      // cost of `gap` consecutive tiles while problem 1 has tiles left
     const int cost_all = (int)(tiles0 * tile_c0 + tiles1 * tile_c1);
-    auto cost_at = [&](long u) -> int {
-        const int ui = (int)u, tile = ui / KBLK, within = ui - tile * KBLK;
+    auto cost_at = [&](int u) -> int {
+        const int tile = u / KBLK, within = u - tile * KBLK;
         const int nb = t1_i > 0 ? (tile / gap_i < t1_i ? tile / gap_i : t1_i) : 0;
         const bool is1 = t1_i > 0 && tile % gap_i == gap_i - 1 && tile / gap_i < t1_i;
         return (tile - nb) * tile_c0 + nb * tile_c1 + within * (is1 ? wc1 : wc0);
     };
-    auto unit_lo = [&](long c) -> long {  // the first unit whose preceding cost reaches c / G of the total (closed form of the inverse of cost_at)
+    auto unit_lo = [&](int c) -> int {  // the first unit whose preceding cost reaches c / G of the total (closed form of the inverse of cost_at)
         if (!a.split_k) return (tiles * c / G) * KBLK;
         if (c <= 0) return 0;
         if (c >= G) return U;
-        const int x = (int)((long)cost_all * c / G);
+        const int x = (int)((long long)cost_all * c / G);  // the one 64-bit division
         int tile, rem, w;
         if (t1_i > 0 && x < t1_i * period_c) {
             const int j = x / period_c, r = x - j * period_c;
@@ -134,9 +134,9 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
             const int y = x - t1_i * period_c, q = y / tile_c0;
             tile = t1_i * gap_i + q; rem = y - q * tile_c0; w = wc0;
         }
-        return (long)tile * KBLK + (rem + w - 1) / w;
+        return tile * KBLK + (rem + w - 1) / w;
     };
-    const long lo = unit_lo(blockIdx.x), hi = unit_lo(blockIdx.x + 1);
+    const int lo = unit_lo(blockIdx.x), hi = unit_lo(blockIdx.x + 1);
     const int nwork0 = (int)(tiles0 / tpw0) > 0 ? (int)(tiles0 / tpw0) : 1, nwork1 = (int)(tiles1 / tpw1) > 0 ? (int)(tiles1 / tpw1) : 1;
     int wstride0 = (int)(nwork0 * 0.618f) | 1;  // near the golden ratio of the list, then the next value coprime to its length
     for (;; ++wstride0) {
@@ -145,16 +145,16 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
         if (x == 1) break;
     }
 
-    struct Seg { long tile; int kb0, kb1, pr, wk, it, e; };
-    auto seg_at = [&](long u) -> Seg {
+    struct Seg { int tile; int kb0, kb1, pr, wk, it, e; };
+    auto seg_at = [&](int u) -> Seg {
         Seg s;
         s.tile = u / KBLK;
         s.kb0 = (int)(u - s.tile * KBLK);
-        const long end = (s.tile + 1) * KBLK;
+        const int end = (s.tile + 1) * KBLK;
         s.kb1 = (int)((end < hi ? end : hi) - s.tile * KBLK);
-        // the tiles of problem 1 (the shared expert: twice the bytes per k block) are spread evenly through the sequence, one after
+        // the tiles of problem 1 (the shared expert) are spread evenly through the sequence, one after
         // every `gap - 1` tiles of problem 0, so that no CTA gets more than its share of them
-        const long nb = s.tile / gap < tiles1 ? s.tile / gap : tiles1;   // tiles of problem 1 before this position
+        const int nb = s.tile / gap < tiles1 ? s.tile / gap : tiles1;   // tiles of problem 1 before this position
         s.pr = (tiles1 > 0 && s.tile % gap == gap - 1 && s.tile / gap < tiles1) ? 1 : 0;
         // Order of a problem's tiles: tile index major, works minor, the works taken with a stride coprime to their number.  Tiles of
         // an expert that many tokens chose cost more (more accumulator rows to move out); consecutive positions of the sequence then
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
         const int nw = s.pr ? nwork1 : nwork0;
         s.it = rel / nw;
         const int j = rel - s.it * nw;
-        s.wk = s.pr ? j : (int)(((long)j * wstride0) % nw);
+        s.wk = s.pr ? j : (j * wstride0) % nw;
         s.e = a.p[s.pr].work ? __ldg(a.p[s.pr].work + s.wk) : 0;
         return s;
     };
@@ -174,10 +174,10 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
     // part LAST: one of those CTAs may lie inside the tile with its whole range and publish only at its end, and a leading part done
     // first would wait for it with the accumulator in hand.  Order: trailing share, whole tiles, leading part.
     const bool has_head = a.split_k && (lo % KBLK != 0) && ((lo / KBLK + 1) * KBLK <= hi);
-    const long head_end = has_head ? (lo / KBLK + 1) * KBLK : lo;  // leading part = [lo, head_end)
-    const long tail_floor = (hi / KBLK) * KBLK;
-    const long tail_start = (a.split_k && hi % KBLK != 0) ? (tail_floor > head_end ? tail_floor : head_end) : hi;  // trailing share = [tail_start, hi)
-    struct It { long u; int ph; bool done; };
+    const int head_end = has_head ? (lo / KBLK + 1) * KBLK : lo;  // leading part = [lo, head_end)
+    const int tail_floor = (hi / KBLK) * KBLK;
+    const int tail_start = (a.split_k && hi % KBLK != 0) ? (tail_floor > head_end ? tail_floor : head_end) : hi;  // trailing share = [tail_start, hi)
+    struct It { int u; int ph; bool done; };
     auto it_enter = [&](It& it, int ph) {  // the first non-empty part from `ph` on
         for (; ph < 3; ++ph) {
             if (ph == 0 && tail_start < hi) { it = It{tail_start, 0, false}; return; }
@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
     };
     auto it_next = [&](It& it, const Seg& sg) {
         if (it.ph == 1) {
-            const long u = sg.tile * KBLK + sg.kb1;
+            const int u = sg.tile * KBLK + sg.kb1;
             if (u < tail_start) { it.u = u; return; }
         }
         it_enter(it, it.ph + 1);
@@ -287,8 +287,8 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                 const WmProb& P = a.p[sg.pr];
                 const bool owner = sg.kb1 == KBLK;
                 wm_epi_bar();  // the tasks of the previous segment are done: its tables and the staging buffer may be overwritten
-                if (et < NT)   // which tokens take part: all of them in a partial tile, the work's table for a finished one
-                    s_slot[et] = !owner ? (uint8_t)1 : (P.slot ? __ldg(P.slot + (size_t)sg.wk * NT + et) : (uint8_t)(et < P.tokens ? 1 : 0));
+                if (et < NT)   // which tokens take part: the work's table, for a share of a tile as for a finished tile (same rows in both)
+                    s_slot[et] = P.slot ? __ldg(P.slot + (size_t)sg.wk * NT + et) : (uint8_t)(et < P.tokens ? 1 : 0);
                 wm_epi_bar();
                 // the taking-part tokens, compacted: s_live[i] = i-th such token, s_pos[t] = its index (-1: token t does not take part)
                 if (ew == 0) {
@@ -305,16 +305,16 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                 if (et == 0) {
                     int np = 0;
                     if (owner && sg.kb0 > 0) {
-                        const long u0 = sg.tile * KBLK;
-                        long c_first = (long)cost_at(u0) * G / cost_all;
-                        if (c_first >= (long)blockIdx.x) c_first = (long)blockIdx.x - 1;
+                        const int u0 = sg.tile * KBLK;
+                        int c_first = (int)((long long)cost_at(u0) * G / cost_all);
+                        if (c_first >= (int)blockIdx.x) c_first = (int)blockIdx.x - 1;
                         if (c_first < 0) c_first = 0;
-                        while (c_first + 1 < (long)blockIdx.x && unit_lo(c_first + 1) <= u0) ++c_first;
+                        while (c_first + 1 < (int)blockIdx.x && unit_lo(c_first + 1) <= u0) ++c_first;
                         while (c_first > 0 && unit_lo(c_first) > u0) --c_first;
-                        long ulo = unit_lo(c_first);
-                        for (long c = c_first; c < (long)blockIdx.x && np < WM_MAX_PRED; ++c) {
-                            const long unext = unit_lo(c + 1);
-                            if (unext != ulo) s_pred[np++] = (uint8_t)((long)blockIdx.x - c);  // a CTA without work leaves nothing
+                        int ulo = unit_lo(c_first);
+                        for (int c = c_first; c < (int)blockIdx.x && np < WM_MAX_PRED; ++c) {
+                            const int unext = unit_lo(c + 1);
+                            if (unext != ulo) s_pred[np++] = (uint8_t)((int)blockIdx.x - c);  // a CTA without work leaves nothing
                             ulo = unext;
                         }
                     }
@@ -387,10 +387,18 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                             const int r = task >> 2, g = task & 3, t = s_live[p0 + r], col = row0 + g * 32 + lane;
                             if (row0 + g * 32 >= a.inter) continue;
                             float gt = stg[(size_t)r * WM_STG_LD + g * 32 + lane], up = stg[(size_t)r * WM_STG_LD + 128 + g * 32 + lane];
-                            for (int pi = 0; pi < n_pred; ++pi) {
-                                const float* src = a.partial + ((size_t)(blockIdx.x - s_pred[pi]) * WM_NT_MAX + t) * WM_TILE_ROWS + g * 32 + lane;
-                                gt += __ldcg(src);
-                                up += __ldcg(src + 128);
+                            for (int pi = 0; pi < n_pred; pi += 4) {  // four shares in flight, added in CTA order
+                                float pg[4], pu[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int pq = pi + q < n_pred ? pi + q : n_pred - 1;
+                                    const float* src = a.partial + ((size_t)(blockIdx.x - s_pred[pq]) * WM_NT_MAX + t) * WM_TILE_ROWS + g * 32 + lane;
+                                    pg[q] = __ldcg(src);
+                                    pu[q] = __ldcg(src + 128);
+                                }
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    if (pi + q < n_pred) { gt += pg[q]; up += pu[q]; }
                             }
                             if (P.round_gu_bf16) { gt = round_bf16(gt); up = round_bf16(up); }
                             const float pw = P.pair_w ? __ldg(P.pair_w + (size_t)t * topk + s_slot[t] - 1) : 1.f;
@@ -415,9 +423,16 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
                                 *reinterpret_cast<float4*>(a.partial + ((size_t)blockIdx.x * WM_NT_MAX + t) * WM_TILE_ROWS + h * 128 + c) = v;
                                 continue;
                             }
-                            for (int pi = 0; pi < n_pred; ++pi) {  // the shares of the CTAs before this one, in CTA order
-                                const float4 p4 = __ldcg(reinterpret_cast<const float4*>(a.partial + ((size_t)(blockIdx.x - s_pred[pi]) * WM_NT_MAX + t) * WM_TILE_ROWS + h * 128 + c));
-                                v.x += p4.x; v.y += p4.y; v.z += p4.z; v.w += p4.w;
+                            for (int pi = 0; pi < n_pred; pi += 4) {  // the shares of the CTAs before this one: four in flight, added in CTA order
+                                float4 p4[4];
+#pragma unroll
+                                for (int q = 0; q < 4; ++q) {
+                                    const int pq = pi + q < n_pred ? pi + q : n_pred - 1;
+                                    p4[q] = __ldcg(reinterpret_cast<const float4*>(a.partial + ((size_t)(blockIdx.x - s_pred[pq]) * WM_NT_MAX + t) * WM_TILE_ROWS + h * 128 + c));
+                                }
+#pragma unroll
+                                for (int q = 0; q < 4; ++q)
+                                    if (pi + q < n_pred) { v.x += p4[q].x; v.y += p4[q].y; v.z += p4[q].z; v.w += p4[q].w; }
                             }
                             if (c >= ok_h[h]) continue;
                             const long orow = has_slot ? (long)t * topk + s_slot[t] - 1 : (long)t;
