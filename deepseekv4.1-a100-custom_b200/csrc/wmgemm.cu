@@ -84,6 +84,11 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
         mbar_init(bar_acc_empty, 1);
         mbar_fence_init();
     }
+    if (tid == 0) {  // the descriptors of the copies: fetched while the kernel before this one is still running
+        tma_prefetch_desc(&tm_w0);
+        tma_prefetch_desc(&tm_x0);
+        if (a.n_prob > 1) { tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_x1); }
+    }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tmem_base_sh), MX_TMEM_COLS);
         tmem_relinquish();
@@ -138,12 +143,8 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
     };
     const int lo = unit_lo(blockIdx.x), hi = unit_lo(blockIdx.x + 1);
     const int nwork0 = (int)(tiles0 / tpw0) > 0 ? (int)(tiles0 / tpw0) : 1, nwork1 = (int)(tiles1 / tpw1) > 0 ? (int)(tiles1 / tpw1) : 1;
-    int wstride0 = (int)(nwork0 * 0.618f) | 1;  // near the golden ratio of the list, then the next value coprime to its length
-    for (;; ++wstride0) {
-        int x = wstride0, y = nwork0;
-        while (y) { const int t = x % y; x = y; y = t; }
-        if (x == 1) break;
-    }
+    // a prime that does not divide the length of the list is coprime to it (three candidates: their product exceeds any list)
+    const int wstride0 = nwork0 % 29 ? 29 : (nwork0 % 31 ? 31 : 37);
 
     struct Seg { int tile; int kb0, kb1, pr, wk, it, e; };
     auto seg_at = [&](int u) -> Seg {
@@ -203,9 +204,6 @@ __global__ void __launch_bounds__(WM_THREADS, 1) wm_gemm_kernel(const WmArgs a, 
         if (warp == 0) {
             // ------------------------------------------------ copy producer (one thread)
             if (lane == 0) {
-                tma_prefetch_desc(&tm_w0);
-                tma_prefetch_desc(&tm_x0);
-                if (a.n_prob > 1) { tma_prefetch_desc(&tm_w1); tma_prefetch_desc(&tm_x1); }
                 uint32_t n = 0, s = 0, ph = 0;  // k blocks issued, their stage and the stage's phase
                 for (It it = it_begin(); !it.done && !abort_flag;) {
                     const Seg sg = seg_at(it.u);
