@@ -76,7 +76,7 @@ class MoELayer:
 
     def dominant_kernel(self, tokens: int) -> str:
         if self._use_mx(tokens) and self._atoms is not None and tokens <= 64:
-            return "wm_gemm_kernel (gate/up weight stream of the routed experts and the shared expert, weight rows on the M side of tcgen05 kind::mxf8f6f4 tiles, k range cut evenly over the SMs, + SwiGLU + FP8 quant)"
+            return "wm_gemm_kernel (gate/up weight stream of the routed experts and the shared expert, tokens on the M side and 256 weight rows on the N side of tcgen05 kind::mxf8f6f4 tiles, the k blocks of all tiles cut evenly over the SMs)"
         if self._use_mx(tokens):
             return "mx_gemm_kernel (gate/up weight stream of the routed experts and the shared expert on tcgen05 kind::mxf8f6f4 + SwiGLU + FP8 quant)"
         return "skinny_kernel<FP4_E8M0, SWIGLU> (routed gate/up weight stream + SwiGLU + FP8 fake quant)"
