@@ -4,8 +4,9 @@
  *
  * Conventions (the ones dsv41/cukern.py:1-57 sets for the reference's launchers):
  *   - every pointer is a DEVICE pointer on the current CUDA device unless the comment says "host";
- *   - every call only enqueues work on `stream` and nothing allocates.  The one call that synchronises is
- *     b200_device_error (it waits for `stream` and reads the device error word).  Scratch memory is passed in
+ *   - every call that takes a `stream` only enqueues work on it and nothing allocates.  The one such call that synchronises is
+ *     b200_device_error (it waits for `stream` and reads the device error word); the set-up calls without a stream argument
+ *     (b200_ep_alloc / _free / _export / _open / _close, b200_set_wait_limit_ns) may allocate and synchronise.  Scratch memory is passed in
  *     by the caller (`workspace`), sized by the matching *_workspace_bytes function, except for
  *     b200_fp4_grouped_gemm_static, whose scratch is a fixed array inside the library;
  *   - b200_hc_post2 and b200_sum_rows put rows / groups on the grid's y dimension: at most 65,535 of them per call;
