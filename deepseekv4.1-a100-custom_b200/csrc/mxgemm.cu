@@ -476,7 +476,7 @@ __global__ void mx_quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, lon
 
 // 16-byte-aligned rows: a thread quantises 8 values (one 16-byte load) of MXQ_ROWS consecutive output rows, 4 threads share a group of
 // 32.  The row indices and then the loads of all its rows are in flight together: with one row per thread the kernel is a chain of two
-// dependent loads per thread and as many waves of threads as it takes (92 us for 28,672 rows of 4096; 4 rows per thread: see the profile).
+// dependent loads per thread and as many waves of threads as it takes (92 us for 28,672 rows of 4096 values; with 4 rows per thread 65 us).
 // Two row sets in one launch: rows [0, rows) gather input rows through src_row (or take row r when src_row is null) into q8 / sf, rows
 // [rows, rows + rows2) take input row r - rows into q8b / sfb (the layer quantises its pair-sorted copy and its token-order copy in one go).
 constexpr int MXQ_ROWS = 4;
