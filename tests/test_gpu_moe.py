@@ -145,6 +145,22 @@ def test_shared_expert_for_a_row_range_only(mods, dev, T, rows):
         layer.forward(x, logits, shared_rows=rows)  # only for calls that do not form the final output
 
 
+@pytest.mark.parametrize("T", [1, 5, 40, 200])
+def test_shard_that_no_token_routes_to(mods, dev, T):
+    # a rank whose experts nobody chose: its routed partial sum is exactly zero, the shared expert still comes out right
+    E, D, I, topk = 16, 512, 256, 4
+    _, _, full = _layer(mods, dev, E, D, I, topk, 31)
+    _, _, part = _layer(mods, dev, E, D, I, topk, 31, shard=(12, 4))
+    x = mods.synth.make_tokens(T, D, 37).to(dev)
+    logits = mods.synth.make_logits(T, E, 38, topk=topk).to(dev)
+    logits[:, 12:] = -50.0  # experts 12..15 never make the top 4
+    routed, ys = part.forward(x, logits, final=False, want_routed=True, want_shared=True)
+    assert torch.count_nonzero(routed) == 0
+    _, ys_full = full.forward(x, logits, final=False, want_routed=True, want_shared=True)
+    assert torch.equal(ys, ys_full)
+    assert mods.cukern.device_error(dev) == 0
+
+
 def test_expert_parallel_layer_world_of_one_equals_layer(mods, dev):
     # the CUDA defaults of the expert-parallel wrapper (shared expert fused into the local launches) on a one-rank group
     import os
