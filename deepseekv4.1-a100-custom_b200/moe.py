@@ -84,7 +84,7 @@ class MoELayer:
     def traffic_ratio(self, tokens: int) -> float:
         """DRAM bytes (read + write) per algorithmic byte of the dominant kernel, from the profiler captures of a smaller case
         (profiles/wm_gemm_kernel_decode64_e96_ncu_full.md, profiles/skinny_fp4_decode8_ncu_full.md)."""
-        return 1.067 if self._use_mx(tokens) else 1.075
+        return 1.057 if self._use_mx(tokens) else 1.075
 
     def shared_expert(self, x: torch.Tensor) -> torch.Tensor | None:
         """The shared expert alone: x bf16 [T, D] -> ys bf16 [T, D] (None without one); the values of dsv41/model.py:1635-1638 on FP8
