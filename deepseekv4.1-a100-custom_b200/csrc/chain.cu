@@ -405,23 +405,26 @@ __global__ void __launch_bounds__(256) dq_swiglu_kernel(const DqSwigluArgs a) {
         atoms = a.hs_atoms;
         round_gu = 1;  // the shared expert's gate / up values pass through bf16 (dsv41/model.py:1635-1638)
     }
-    for (int g0 = warp; g0 < (I >> 5); g0 += 32) {  // four groups per warp and pass: independent chains in flight
-        float h[4], amax[4];
+    for (int g0 = warp; g0 < (I >> 5); g0 += 64) {  // eight groups per warp and pass, their 16 loads in flight together
+        float gt[8], up[8], h[8], amax[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
             const int g = g0 + 8 * u;
-            float gt = 0.f, up = 0.f;
-            if (g < (I >> 5)) { gt = __ldcg(src + g * 32 + lane); up = __ldcg(src + I + g * 32 + lane); }
-            if (round_gu) { gt = round_bf16(gt); up = round_bf16(up); }
-            h[u] = swiglu_bf16(gt, up, w, a.limit);
+            gt[u] = up[u] = 0.f;
+            if (g < (I >> 5)) { gt[u] = __ldcg(src + g * 32 + lane); up[u] = __ldcg(src + I + g * 32 + lane); }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (round_gu) { gt[u] = round_bf16(gt[u]); up[u] = round_bf16(up[u]); }
+            h[u] = swiglu_bf16(gt[u], up[u], w, a.limit);
             amax[u] = fabsf(h[u]);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
+            for (int u = 0; u < 8; ++u) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 8; ++u) {
             const int g = g0 + 8 * u;
             if (g >= (I >> 5)) continue;
             const uint32_t sb = (f32_as_u32(fp8_group_scale_bf16(amax[u])) >> 23) & 0xFFu;
@@ -518,6 +521,55 @@ __global__ void moe_combine_kernel(const float* __restrict__ y2, const int* __re
     }
     if (routed) routed[i] = acc;
     if (out) out[i] = __float2bfloat16_rn(acc + (ys ? __bfloat162float(ys[i]) : 0.f));
+}
+
+// the same with four columns per thread: the top-k slots of a token are read with all their loads in flight (dim % 4 == 0, topk <= 8,
+// 16-byte aligned rows); the order of the additions is that of the scalar kernel (slot order)
+__global__ void moe_combine_vec_kernel(const float* __restrict__ y2, const int* __restrict__ eid, const __nv_bfloat16* __restrict__ ys,
+                                       __nv_bfloat16* __restrict__ out, float* __restrict__ routed, int tokens, int topk, int dim, int shard_start,
+                                       int shard_n) {
+    pdl_wait();
+    const int d4 = dim >> 2;
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)tokens * d4) return;
+    const int t = (int)(i / d4), n = (int)(i - (long)t * d4) * 4;
+    float4 v[8];
+    bool on[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        on[j] = false;
+        if (j < topk) {
+            const int e = __ldg(eid + t * topk + j);
+            on[j] = e >= shard_start && e < shard_start + shard_n;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        v[j] = on[j] ? __ldcg(reinterpret_cast<const float4*>(y2 + ((long)t * topk + j) * dim + n)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if (on[j]) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+    if (routed) *reinterpret_cast<float4*>(routed + (long)t * dim + n) = acc;
+    if (out) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        if (ys) {
+            const uint2 y = *reinterpret_cast<const uint2*>(ys + (long)t * dim + n);
+            s0 = bf16_bits_to_f32(y.x & 0xFFFFu); s1 = bf16_bits_to_f32(y.x >> 16); s2 = bf16_bits_to_f32(y.y & 0xFFFFu); s3 = bf16_bits_to_f32(y.y >> 16);
+        }
+        *reinterpret_cast<uint2*>(out + (long)t * dim + n) = make_uint2(f32_to_bf16_bits(acc.x + s0) | (f32_to_bf16_bits(acc.y + s1) << 16),
+                                                                        f32_to_bf16_bits(acc.z + s2) | (f32_to_bf16_bits(acc.w + s3) << 16));
+    }
+}
+
+static cudaError_t launch_combine(const float* y2, const int* eid, const __nv_bfloat16* ys, __nv_bfloat16* out, float* routed, int tokens, int topk, int dim,
+                                  int shard_start, int shard_n, cudaStream_t stream) {
+    const long n = (long)tokens * dim;
+    if (dim % 4 == 0 && topk <= 8 && !(((uintptr_t)y2 | (uintptr_t)routed) & 15) && !(((uintptr_t)ys | (uintptr_t)out) & 7))
+        return launch_pdl(moe_combine_vec_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, stream, y2, eid, ys, out, routed, tokens, topk, dim,
+                          shard_start, shard_n);
+    return launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, y2, eid, ys, out, routed, tokens, topk, dim, shard_start,
+                      shard_n);
 }
 
 struct Carver {
@@ -809,9 +861,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
             q.epi = WM_EPI_STORE_BF16; q.out = ys_buf; q.out_ld = D;
         }
         if ((rc = wm_launch(g2, stream))) return rc;
-        const long n = (long)T * D;
-        if ((ce = launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.y2, (const int*)w.eid,
-                             (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, m->routed_out, T, topk, D, m->shard_start, shard_n)) != cudaSuccess)
+        if ((ce = launch_combine((const float*)w.y2, (const int*)w.eid, (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, m->routed_out,
+                                 T, topk, D, m->shard_start, shard_n, stream)) != cudaSuccess)
             return (int)ce;
         if (m->eid_out && (ce = cudaMemcpyAsync(m->eid_out, w.eid, P * sizeof(int), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
         if (m->wt_out && (ce = cudaMemcpyAsync(m->wt_out, w.wt, P * sizeof(float), cudaMemcpyDeviceToDevice, stream)) != cudaSuccess) return (int)ce;
@@ -959,9 +1010,8 @@ extern "C" int b200_moe_forward(const b200_moe_args* m, cudaStream_t stream) {
     // ---- combine: routed sum (+ shared expert) -> bf16
     const long n = (long)T * D;
     if (small) {
-        if ((ce = launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)w.y2, (const int*)w.eid,
-                             (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, m->routed_out, T, topk, D, m->shard_start, shard_n)) !=
-            cudaSuccess)
+        if ((ce = launch_combine((const float*)w.y2, (const int*)w.eid, (const __nv_bfloat16*)(shared ? ys_buf : nullptr), (__nv_bfloat16*)m->out, m->routed_out,
+                                 T, topk, D, m->shard_start, shard_n, stream)) != cudaSuccess)
             return (int)ce;
     } else {
         if (m->out) {
